@@ -1,0 +1,503 @@
+// Inclusive scan (cumsum) for sm_100a.
+//
+// Flat form (rows == 1): a single pass over the data with decoupled look-back.  The array is cut
+// into tiles of THREADS*16 elements; persistent CTAs draw tile numbers from an atomic ticket (so a
+// tile only ever waits on tiles that are already running), scan their tile in registers, publish
+// the tile aggregate, look back over the predecessors' descriptors to obtain the exclusive prefix,
+// publish the inclusive prefix and write the result.  Traffic is one read and one write of the
+// array; descriptors are 8 bytes per tile ({flag, value} in one 64-bit word, read and written with
+// single relaxed gpu-scope accesses, so no fence is needed).  Every wait on a descriptor is bounded;
+// when the bound is hit the kernel raises the device error word and finishes without waiting.
+//
+// Row form: one CTA per row walks the row tile by tile with a running carry.  The reference scans
+// one whole row per tile (examples/10_cumsum.py:17-25); rows here may be any length.
+//
+// Accumulation follows tl.cumsum (src/enceladus/language/ops.py:2047-2060): integers up to 32 bits in
+// 32-bit two's-complement arithmetic (unsigned adds, so the wrap is defined), float16/bfloat16/
+// float32 in float32, int64 in int64.
+#include <map>
+#include <mutex>
+
+#include "common.cuh"
+
+namespace enc {
+namespace {
+
+constexpr int QUADS = 4;                 // quads (4 consecutive elements) per thread per tile
+constexpr int ITEMS = QUADS * 4;         // elements per thread per tile
+constexpr unsigned FLAG_EMPTY = 0, FLAG_AGGREGATE = 1, FLAG_PREFIX = 2;
+constexpr unsigned SPIN_LIMIT = 1u << 20;  // polls of one descriptor before giving up
+
+// ---- element access ------------------------------------------------------------------------
+template <typename T> struct AccOf { using type = float; };
+template <> struct AccOf<int> { using type = unsigned; };
+template <> struct AccOf<signed char> { using type = unsigned; };
+template <> struct AccOf<unsigned char> { using type = unsigned; };
+template <> struct AccOf<short> { using type = unsigned; };
+template <> struct AccOf<long long> { using type = unsigned long long; };
+
+template <typename T> struct OutOf { using type = T; };
+template <> struct OutOf<signed char> { using type = int; };
+template <> struct OutOf<unsigned char> { using type = int; };
+template <> struct OutOf<short> { using type = int; };
+
+template <typename Acc, typename T> __device__ __forceinline__ Acc to_acc(T v) { return (Acc)v; }
+template <> __device__ __forceinline__ float to_acc<float, __half>(__half v) { return __half2float(v); }
+template <> __device__ __forceinline__ float to_acc<float, __nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
+template <> __device__ __forceinline__ unsigned to_acc<unsigned, signed char>(signed char v) { return (unsigned)(int)v; }
+template <> __device__ __forceinline__ unsigned to_acc<unsigned, short>(short v) { return (unsigned)(int)v; }
+
+template <typename T, typename Acc> __device__ __forceinline__ T from_acc(Acc v) { return (T)v; }
+template <> __device__ __forceinline__ int from_acc<int, unsigned>(unsigned v) { return (int)v; }
+template <> __device__ __forceinline__ __half from_acc<__half, float>(float v) { return __float2half_rn(v); }
+template <> __device__ __forceinline__ __nv_bfloat16 from_acc<__nv_bfloat16, float>(float v) { return __float2bfloat16_rn(v); }
+
+template <typename T, int BYTES> struct alignas(BYTES) Quad { T v[4]; };
+
+template <typename T, typename Acc>
+__device__ __forceinline__ void load_quad(const T *p, Acc *a) {
+    Quad<T, 4 * sizeof(T)> q = *reinterpret_cast<const Quad<T, 4 * sizeof(T)> *>(p);
+#pragma unroll
+    for (int e = 0; e < 4; ++e) a[e] = to_acc<Acc, T>(q.v[e]);
+}
+template <typename T, typename Acc>
+__device__ __forceinline__ void store_quad(T *p, const Acc *a) {
+    Quad<T, 4 * sizeof(T)> q;
+#pragma unroll
+    for (int e = 0; e < 4; ++e) q.v[e] = from_acc<T, Acc>(a[e]);
+    *reinterpret_cast<Quad<T, 4 * sizeof(T)> *>(p) = q;
+}
+
+// ---- scan of one tile held in registers ----------------------------------------------------
+// v[j][e] is element (j*THREADS + thread)*4 + e of the tile.  On return v holds the inclusive scan
+// of the tile (no external prefix); the function returns the tile total to every thread.
+template <typename Acc, int THREADS>
+__device__ __forceinline__ Acc tile_scan(Acc (&v)[QUADS][4], Acc *sh /* [QUADS * THREADS/32 + 1] */) {
+    constexpr int NW = THREADS / 32;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    Acc incl[QUADS];
+#pragma unroll
+    for (int j = 0; j < QUADS; ++j) {
+        v[j][1] += v[j][0]; v[j][2] += v[j][1]; v[j][3] += v[j][2];
+        incl[j] = v[j][3];
+    }
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+#pragma unroll
+        for (int j = 0; j < QUADS; ++j) {
+            const Acc up = __shfl_up_sync(0xffffffffu, incl[j], o);
+            if (lane >= o) incl[j] += up;
+        }
+    }
+    Acc before[QUADS];  // sum of the quads of the lanes before me, per slab
+#pragma unroll
+    for (int j = 0; j < QUADS; ++j) {
+        before[j] = __shfl_up_sync(0xffffffffu, incl[j], 1);
+        if (lane == 0) before[j] = 0;
+    }
+    __syncthreads();  // sh may still be read by the previous tile's consumers
+    if (lane == 31) {
+#pragma unroll
+        for (int j = 0; j < QUADS; ++j) sh[j * NW + warp] = incl[j];
+    }
+    __syncthreads();
+    if (warp == 0) {
+        // exclusive scan of the QUADS*NW warp totals (slab-major order), K consecutive per lane
+        constexpr int K = QUADS * NW / 32;
+        Acc loc[K > 0 ? K : 1];
+        Acc run = 0;
+#pragma unroll
+        for (int k = 0; k < K; ++k) { loc[k] = sh[lane * K + k]; run += loc[k]; }
+        Acc inc = run;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const Acc up = __shfl_up_sync(0xffffffffu, inc, o);
+            if (lane >= o) inc += up;
+        }
+        Acc ex = __shfl_up_sync(0xffffffffu, inc, 1);  // exclusive = previous lane's inclusive
+        if (lane == 0) ex = 0;
+#pragma unroll
+        for (int k = 0; k < K; ++k) { sh[lane * K + k] = ex; ex += loc[k]; }
+        if (lane == 31) sh[QUADS * NW] = inc;  // tile total
+    }
+    __syncthreads();
+#pragma unroll
+    for (int j = 0; j < QUADS; ++j) {
+        const Acc base = sh[j * NW + warp] + before[j];  // warps before mine + lanes before me
+#pragma unroll
+        for (int e = 0; e < 4; ++e) v[j][e] += base;
+    }
+    return sh[QUADS * NW];
+}
+
+// ---- descriptors ---------------------------------------------------------------------------
+__device__ __forceinline__ void desc_store(unsigned long long *p, unsigned flag, unsigned value) {
+    const unsigned long long w = ((unsigned long long)flag << 32) | value;
+    asm volatile("st.relaxed.gpu.global.u64 [%0], %1;" :: "l"(p), "l"(w) : "memory");
+}
+__device__ __forceinline__ unsigned long long desc_load(const unsigned long long *p) {
+    unsigned long long w;
+    asm volatile("ld.relaxed.gpu.global.u64 %0, [%1];" : "=l"(w) : "l"(p) : "memory");
+    return w;
+}
+__device__ __forceinline__ unsigned bits_of(unsigned v) { return v; }
+__device__ __forceinline__ unsigned bits_of(float v) { return __float_as_uint(v); }
+template <typename Acc> __device__ __forceinline__ Acc acc_of_bits(unsigned b);
+template <> __device__ __forceinline__ unsigned acc_of_bits<unsigned>(unsigned b) { return b; }
+template <> __device__ __forceinline__ float acc_of_bits<float>(unsigned b) { return __uint_as_float(b); }
+
+struct FlatArgs {
+    const void *in;
+    void *out;
+    int64_t n;
+    const void *seed;
+    unsigned long long *desc;  // one word per tile, zeroed before the launch
+    unsigned *ticket;          // zeroed before the launch
+    unsigned *error;           // device error word (sticky)
+    int vec;                   // base pointers aligned for quad accesses
+};
+
+template <typename TIn, typename Acc, typename TOut, int THREADS>
+__global__ void __launch_bounds__(THREADS) scan_lookback_kernel(FlatArgs a) {
+    constexpr int TILE = THREADS * ITEMS;
+    constexpr int NW = THREADS / 32;
+    __shared__ Acc sh[QUADS * NW + 1];
+    __shared__ unsigned s_tile;
+    __shared__ Acc s_prefix;
+    const TIn *in = reinterpret_cast<const TIn *>(a.in);
+    TOut *out = reinterpret_cast<TOut *>(a.out);
+    const int64_t ntiles = (a.n + TILE - 1) / TILE;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+
+    for (;;) {
+        if (threadIdx.x == 0) s_tile = atomicAdd(a.ticket, 1u);
+        __syncthreads();
+        const int64_t tile = s_tile;
+        if (tile >= ntiles) break;
+        const int64_t t0 = tile * TILE;
+        const bool full = a.vec && t0 + TILE <= a.n;
+
+        Acc v[QUADS][4];
+#pragma unroll
+        for (int j = 0; j < QUADS; ++j) {
+            const int64_t i0 = t0 + ((int64_t)j * THREADS + threadIdx.x) * 4;
+            if (full) {
+                load_quad<TIn, Acc>(in + i0, v[j]);
+            } else {
+#pragma unroll
+                for (int e = 0; e < 4; ++e) v[j][e] = i0 + e < a.n ? to_acc<Acc, TIn>(in[i0 + e]) : Acc(0);
+            }
+        }
+        const Acc total = tile_scan<Acc, THREADS>(v, sh);
+
+        if (warp == 0) {
+            Acc exclusive = 0;
+            if (tile == 0) {
+                if (a.seed) exclusive = *reinterpret_cast<const Acc *>(a.seed);
+                if (lane == 0) desc_store(a.desc, FLAG_PREFIX, bits_of(Acc(exclusive + total)));
+            } else {
+                if (lane == 0) desc_store(a.desc + tile, FLAG_AGGREGATE, bits_of(total));
+                int64_t look = tile - 1;  // lane 0 inspects the nearest predecessor
+                bool done = false;
+                while (!done) {
+                    const int64_t idx = look - lane;
+                    unsigned flag = FLAG_PREFIX, bits = 0;  // "before tile 0" acts as a zero prefix
+                    if (idx >= 0) {
+                        unsigned spins = 0;
+                        for (;;) {
+                            const unsigned long long w = desc_load(a.desc + idx);
+                            flag = (unsigned)(w >> 32);
+                            bits = (unsigned)w;
+                            if (flag != FLAG_EMPTY) break;
+                            if (++spins > SPIN_LIMIT) {  // give up: flag the error, stop waiting
+                                atomicExch(a.error, 1u);
+                                flag = FLAG_PREFIX;
+                                bits = 0;
+                                break;
+                            }
+                            __nanosleep(32);
+                        }
+                    }
+                    const unsigned has_prefix = __ballot_sync(0xffffffffu, flag == FLAG_PREFIX);
+                    // lanes nearer than the first PREFIX contribute aggregates; that lane its prefix
+                    const int stop = has_prefix ? __ffs(has_prefix) - 1 : 31;
+                    Acc contrib = lane <= stop ? acc_of_bits<Acc>(bits) : Acc(0);
+#pragma unroll
+                    for (int o = 16; o > 0; o >>= 1) contrib += __shfl_xor_sync(0xffffffffu, contrib, o);
+                    exclusive += contrib;
+                    done = has_prefix != 0;
+                    look -= 32;
+                }
+                if (lane == 0) desc_store(a.desc + tile, FLAG_PREFIX, bits_of(Acc(exclusive + total)));
+            }
+            if (lane == 0) s_prefix = exclusive;
+        }
+        __syncthreads();
+        const Acc prefix = s_prefix;
+#pragma unroll
+        for (int j = 0; j < QUADS; ++j) {
+            const int64_t i0 = t0 + ((int64_t)j * THREADS + threadIdx.x) * 4;
+#pragma unroll
+            for (int e = 0; e < 4; ++e) v[j][e] += prefix;
+            if (full) {
+                store_quad<TOut, Acc>(out + i0, v[j]);
+            } else {
+#pragma unroll
+                for (int e = 0; e < 4; ++e)
+                    if (i0 + e < a.n) out[i0 + e] = from_acc<TOut, Acc>(v[j][e]);
+            }
+        }
+    }
+}
+
+// ---- row form ------------------------------------------------------------------------------
+struct RowScanArgs {
+    const void *in;
+    void *out;
+    int64_t rows, cols, stride_in, stride_out;
+    int reverse;
+    int vec;
+};
+
+template <typename TIn, typename Acc, typename TOut, int THREADS>
+__global__ void __launch_bounds__(THREADS) scan_rows_kernel(RowScanArgs a) {
+    constexpr int TILE = THREADS * ITEMS;
+    constexpr int NW = THREADS / 32;
+    __shared__ Acc sh[QUADS * NW + 1];
+    const int64_t row = blockIdx.x;
+    const TIn *in = reinterpret_cast<const TIn *>(a.in) + row * a.stride_in;
+    TOut *out = reinterpret_cast<TOut *>(a.out) + row * a.stride_out;
+    const bool rev = a.reverse != 0;
+    Acc carry = 0;
+    for (int64_t t0 = 0; t0 < a.cols; t0 += TILE) {
+        const bool full = a.vec && !rev && t0 + TILE <= a.cols;
+        Acc v[QUADS][4];
+#pragma unroll
+        for (int j = 0; j < QUADS; ++j) {
+            const int64_t i0 = t0 + ((int64_t)j * THREADS + threadIdx.x) * 4;
+            if (full) {
+                load_quad<TIn, Acc>(in + i0, v[j]);
+            } else {
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const int64_t i = i0 + e;  // position in scan order; mirrored when reversed
+                    v[j][e] = i < a.cols ? to_acc<Acc, TIn>(in[rev ? a.cols - 1 - i : i]) : Acc(0);
+                }
+            }
+        }
+        const Acc total = tile_scan<Acc, THREADS>(v, sh);
+#pragma unroll
+        for (int j = 0; j < QUADS; ++j) {
+            const int64_t i0 = t0 + ((int64_t)j * THREADS + threadIdx.x) * 4;
+#pragma unroll
+            for (int e = 0; e < 4; ++e) v[j][e] += carry;
+            if (full) {
+                store_quad<TOut, Acc>(out + i0, v[j]);
+            } else {
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const int64_t i = i0 + e;
+                    if (i < a.cols) out[rev ? a.cols - 1 - i : i] = from_acc<TOut, Acc>(v[j][e]);
+                }
+            }
+        }
+        carry += total;
+    }
+}
+
+// ---- total (pass 1 of the multi-GPU flat scan) ---------------------------------------------
+template <typename TIn, typename Acc>
+__global__ void __launch_bounds__(256) sum_partials_kernel(const TIn *in, int64_t n, Acc *partials) {
+    __shared__ Acc sh[8];
+    Acc s = 0;
+    const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) s += to_acc<Acc, TIn>(in[i]);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+    if ((threadIdx.x & 31) == 0) sh[threadIdx.x >> 5] = s;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        Acc t = 0;
+        for (int i = 0; i < 8; ++i) t += sh[i];
+        partials[blockIdx.x] = t;
+    }
+}
+template <typename Acc>
+__global__ void __launch_bounds__(1024) sum_final_kernel(const Acc *partials, int count, Acc *total) {
+    __shared__ Acc sh[32];
+    Acc s = 0;
+    for (int i = threadIdx.x; i < count; i += blockDim.x) s += partials[i];
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+    if ((threadIdx.x & 31) == 0) sh[threadIdx.x >> 5] = s;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        Acc t = 0;
+        for (int i = 0; i < 32; ++i) t += sh[i];
+        *total = t;
+    }
+}
+
+// ---- scratch -------------------------------------------------------------------------------
+// One buffer per (device, stream): launches on one stream are ordered, so they can share it.
+struct Scratch { void *ptr = nullptr; size_t bytes = 0; };
+std::mutex g_scratch_mu;
+std::map<std::pair<int, void *>, Scratch> g_scratch;
+
+void *scratch_get(size_t bytes, void *stream) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    std::lock_guard<std::mutex> lock(g_scratch_mu);
+    Scratch &s = g_scratch[{dev, stream}];
+    if (s.bytes < bytes) {
+        if (s.ptr) {
+            cudaStreamSynchronize(as_stream(stream));  // earlier launches may still use it
+            cudaFree(s.ptr);
+        }
+        s.ptr = nullptr;
+        s.bytes = 0;
+        size_t want = bytes < (1u << 20) ? (1u << 20) : bytes;
+        if (cudaMalloc(&s.ptr, want) != cudaSuccess) {
+            cudaGetLastError();
+            s.ptr = nullptr;
+            return nullptr;
+        }
+        s.bytes = want;
+    }
+    return s.ptr;
+}
+
+// variant v: CTA threads = {256, 512, 1024}[v]  (tile = threads * 16 elements)
+constexpr int SCAN_VARIANTS = 3;
+
+template <typename TIn, int THREADS>
+int launch_flat_t(const void *in, void *out, int64_t n, const void *seed, cudaStream_t st, void *stream) {
+    using Acc = typename AccOf<TIn>::type;
+    using TOut = typename OutOf<TIn>::type;
+    constexpr int TILE = THREADS * ITEMS;
+    const int64_t ntiles = cdiv(n, TILE);
+    const size_t bytes = 64 + (size_t)ntiles * 8;
+    char *scr = (char *)scratch_get(bytes, stream);
+    if (!scr) return fail(ENC_ERR_NO_MEMORY, "enc_cumsum: cannot allocate %zu bytes of tile descriptors", bytes);
+    unsigned *err = device_error_word();
+    if (!err) return fail(ENC_ERR_NO_MEMORY, "enc_cumsum: cannot allocate the device status word");
+    cudaError_t e = cudaMemsetAsync(scr, 0, bytes, st);
+    if (e != cudaSuccess) return fail(ENC_ERR_LAUNCH, "enc_cumsum: memset of descriptors failed: %s", cudaGetErrorString(e));
+    FlatArgs a{in, out, n, seed, (unsigned long long *)(scr + 64), (unsigned *)scr, err,
+               (reinterpret_cast<uintptr_t>(in) % (4 * sizeof(TIn)) == 0 && reinterpret_cast<uintptr_t>(out) % (4 * sizeof(TOut)) == 0) ? 1 : 0};
+    int64_t grid = (int64_t)device_props().sm_count * (2048 / THREADS);
+    if (grid > ntiles) grid = ntiles;
+    scan_lookback_kernel<TIn, Acc, TOut, THREADS><<<(unsigned)grid, THREADS, 0, st>>>(a);
+    return check_launch("enc_cumsum");
+}
+
+template <typename TIn, int THREADS>
+int launch_rows_t(const void *in, void *out, int64_t rows, int64_t cols, int64_t si, int64_t so, int reverse, cudaStream_t st) {
+    using Acc = typename AccOf<TIn>::type;
+    using TOut = typename OutOf<TIn>::type;
+    const bool vec = reinterpret_cast<uintptr_t>(in) % (4 * sizeof(TIn)) == 0 && reinterpret_cast<uintptr_t>(out) % (4 * sizeof(TOut)) == 0 &&
+                     si % 4 == 0 && so % 4 == 0;
+    RowScanArgs a{in, out, rows, cols, si, so, reverse, vec ? 1 : 0};
+    scan_rows_kernel<TIn, Acc, TOut, THREADS><<<(unsigned)rows, THREADS, 0, st>>>(a);
+    return check_launch("enc_cumsum");
+}
+
+template <typename TIn, bool LOOKBACK>
+int launch_scan(const void *in, void *out, int64_t rows, int64_t cols, int64_t si, int64_t so, int reverse,
+                const void *seed, int variant, void *stream) {
+    cudaStream_t st = as_stream(stream);
+    if (rows == 0 || cols == 0) return ENC_OK;
+    if constexpr (LOOKBACK) {
+        if (rows == 1 && !reverse) {
+            switch (variant < 0 ? 1 : variant) {
+                case 0: return launch_flat_t<TIn, 256>(in, out, cols, seed, st, stream);
+                case 1: return launch_flat_t<TIn, 512>(in, out, cols, seed, st, stream);
+                default: return launch_flat_t<TIn, 1024>(in, out, cols, seed, st, stream);
+            }
+        }
+    }
+    if (seed) return fail(ENC_ERR_UNSUPPORTED, "enc_cumsum: a seed is supported only for the forward flat form (rows == 1) of 32-bit accumulators");
+    if (rows > 0x7fffffffLL) return fail(ENC_ERR_UNSUPPORTED, "enc_cumsum: more than 2^31-1 rows");
+    // Short rows use small CTAs so that a row does not idle most of its threads.
+    int threads = variant < 0 ? (cols <= 4096 ? 256 : cols <= 8192 ? 512 : 1024) : (256 << variant);
+    switch (threads) {
+        case 256: return launch_rows_t<TIn, 256>(in, out, rows, cols, si, so, reverse, st);
+        case 512: return launch_rows_t<TIn, 512>(in, out, rows, cols, si, so, reverse, st);
+        default: return launch_rows_t<TIn, 1024>(in, out, rows, cols, si, so, reverse, st);
+    }
+}
+
+template <typename TIn>
+int launch_sum(const void *in, void *total, int64_t n, void *stream) {
+    using Acc = typename AccOf<TIn>::type;
+    cudaStream_t st = as_stream(stream);
+    int64_t grid = (int64_t)device_props().sm_count * 8;
+    const int64_t need = cdiv(n > 0 ? n : 1, 256 * 8);
+    if (grid > need) grid = need;
+    Acc *partials = (Acc *)scratch_get((size_t)grid * sizeof(Acc), stream);
+    if (!partials) return fail(ENC_ERR_NO_MEMORY, "enc_sum: cannot allocate scratch");
+    sum_partials_kernel<TIn, Acc><<<(unsigned)grid, 256, 0, st>>>((const TIn *)in, n, partials);
+    sum_final_kernel<Acc><<<1, 1024, 0, st>>>(partials, (int)grid, (Acc *)total);
+    return check_launch("enc_sum");
+}
+
+}  // namespace
+
+int scan_variants() { return SCAN_VARIANTS; }
+void scan_variant_info(int v, char *out, size_t n) {
+    snprintf(out, n, "cta_threads=%d tile=%d elements", 256 << v, (256 << v) * ITEMS);
+}
+
+void scratch_release_all() {
+    std::lock_guard<std::mutex> lock(g_scratch_mu);
+    for (auto &kv : g_scratch)
+        if (kv.second.ptr) cudaFree(kv.second.ptr);
+    g_scratch.clear();
+}
+
+}  // namespace enc
+
+extern "C" int enc_cumsum_out_dtype(int dtype) {
+    switch (dtype) {
+        case ENC_I8: case ENC_U8: case ENC_I16: return ENC_I32;
+        case ENC_F32: case ENC_F16: case ENC_BF16: case ENC_I32: case ENC_I64: return dtype;
+        default: return -1;
+    }
+}
+
+extern "C" int enc_cumsum(const void *in, void *out, int64_t rows, int64_t cols, int64_t stride_in,
+                          int64_t stride_out, int reverse, int dtype, const void *seed, int variant,
+                          void *stream) {
+    ENC_PROLOGUE();
+    if (rows < 0 || cols < 0) return enc::fail(ENC_ERR_BAD_ARG, "enc_cumsum: negative shape");
+    if ((!in || !out) && rows * cols > 0) return enc::fail(ENC_ERR_BAD_ARG, "enc_cumsum: NULL input or output");
+    if (variant >= enc::SCAN_VARIANTS) return enc::fail(ENC_ERR_BAD_ARG, "enc_cumsum: variant %d out of range", variant);
+    if (rows > 1 && (stride_in < cols || stride_out < cols)) return enc::fail(ENC_ERR_BAD_ARG, "enc_cumsum: row stride smaller than the row length");
+    switch (dtype) {
+        case ENC_F32: return enc::launch_scan<float, true>(in, out, rows, cols, stride_in, stride_out, reverse, seed, variant, stream);
+        case ENC_F16: return enc::launch_scan<__half, true>(in, out, rows, cols, stride_in, stride_out, reverse, seed, variant, stream);
+        case ENC_BF16: return enc::launch_scan<__nv_bfloat16, true>(in, out, rows, cols, stride_in, stride_out, reverse, seed, variant, stream);
+        case ENC_I32: return enc::launch_scan<int, true>(in, out, rows, cols, stride_in, stride_out, reverse, seed, variant, stream);
+        case ENC_I8: return enc::launch_scan<signed char, true>(in, out, rows, cols, stride_in, stride_out, reverse, seed, variant, stream);
+        case ENC_U8: return enc::launch_scan<unsigned char, true>(in, out, rows, cols, stride_in, stride_out, reverse, seed, variant, stream);
+        case ENC_I16: return enc::launch_scan<short, true>(in, out, rows, cols, stride_in, stride_out, reverse, seed, variant, stream);
+        case ENC_I64: return enc::launch_scan<long long, false>(in, out, rows, cols, stride_in, stride_out, reverse, seed, variant, stream);
+        default: return enc::fail(ENC_ERR_BAD_ARG, "enc_cumsum: unsupported dtype %d", dtype);
+    }
+}
+
+extern "C" int enc_sum(const void *in, void *total, int64_t n, int dtype, void *stream) {
+    ENC_PROLOGUE();
+    if (!total || (!in && n > 0) || n < 0) return enc::fail(ENC_ERR_BAD_ARG, "enc_sum: bad argument");
+    switch (dtype) {
+        case ENC_F32: return enc::launch_sum<float>(in, total, n, stream);
+        case ENC_F16: return enc::launch_sum<__half>(in, total, n, stream);
+        case ENC_BF16: return enc::launch_sum<__nv_bfloat16>(in, total, n, stream);
+        case ENC_I32: return enc::launch_sum<int>(in, total, n, stream);
+        case ENC_I8: return enc::launch_sum<signed char>(in, total, n, stream);
+        case ENC_U8: return enc::launch_sum<unsigned char>(in, total, n, stream);
+        case ENC_I16: return enc::launch_sum<short>(in, total, n, stream);
+        case ENC_I64: return enc::launch_sum<long long>(in, total, n, stream);
+        default: return enc::fail(ENC_ERR_BAD_ARG, "enc_sum: unsupported dtype %d", dtype);
+    }
+}

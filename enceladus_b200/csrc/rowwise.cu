@@ -1,0 +1,326 @@
+// Row softmax, LayerNorm and RMSNorm for sm_100a.
+//
+// All three are HBM-bound: one read and one write of the matrix.  A row is loaded ONCE with
+// 128-bit streaming loads into registers (up to 32 float values per thread), reduced with warp
+// shuffles plus one shared-memory exchange when a row spans several warps, and written back with
+// 128-bit stores.  Statistics are float32; the LayerNorm variance is the centred second pass
+// computed from the registers, so nothing is re-read.  Rows wider than the register budget take a
+// three-pass kernel that re-reads the row through L2.
+//
+// Arithmetic follows the reference kernels op by op (examples/02_softmax.py:15-24,
+// examples/03_layernorm.py:15-42, examples/06_rmsnorm.py:15-24): true division, 1/sqrt in two
+// roundings, products and sums rounded separately (no FMA contraction) so the only difference from
+// the reference interpreter is the order of the row sums.
+#include "common.cuh"
+
+namespace enc {
+namespace {
+
+constexpr int MAX_WARPS = 32;
+
+struct RowArgs {
+    const void *x;
+    void *y;
+    const void *w;
+    const void *b;
+    float *mean;
+    float *rstd;
+    int64_t rows, cols, stride_x, stride_y;
+    float eps;
+    int tpr;  // threads per row (power of two, 32..512)
+};
+
+enum { OP_SOFTMAX = 0, OP_LAYERNORM = 1, OP_RMSNORM = 2 };
+
+// Reduction over the `tpr` threads that share a row.  `slot` is a per-call shared array so that
+// consecutive reductions need one barrier each.
+template <bool IS_MAX>
+__device__ __forceinline__ float group_reduce(float v, int tpr, float *slot) {
+    v = IS_MAX ? warp_max(v) : warp_sum(v);
+    if (tpr > 32) {
+        const int warp = threadIdx.x >> 5;
+        if ((threadIdx.x & 31) == 0) slot[warp] = v;
+        __syncthreads();
+        const int wpr = tpr >> 5;                     // warps per row
+        const int first = (warp / wpr) * wpr;         // first warp of this row group
+        float r = slot[first];
+        for (int i = 1; i < wpr; ++i) r = IS_MAX ? fmaxf(r, slot[first + i]) : r + slot[first + i];
+        v = r;
+    }
+    return v;
+}
+
+template <typename T, int V, bool VEC, int OP>
+__global__ void __launch_bounds__(512) row_kernel(RowArgs a) {
+    constexpr int NV = Pack<T>::N;
+    __shared__ float red0[MAX_WARPS], red1[MAX_WARPS];
+    const int tpr = a.tpr;
+    const int t = threadIdx.x & (tpr - 1);
+    const int64_t rows_per_cta = blockDim.x / tpr;
+    const int64_t row = (int64_t)blockIdx.x * rows_per_cta + threadIdx.x / tpr;
+    const bool live = row < a.rows;
+    const T *xr = reinterpret_cast<const T *>(a.x) + (live ? row : 0) * a.stride_x;
+    T *yr = reinterpret_cast<T *>(a.y) + (live ? row : 0) * a.stride_y;
+    const float fill = OP == OP_SOFTMAX ? -INFINITY : 0.0f;
+
+    float x[V * NV];
+#pragma unroll
+    for (int j = 0; j < V; ++j) {
+        const int64_t c0 = ((int64_t)j * tpr + t) * NV;
+        if (VEC) {
+            if (c0 < a.cols) {
+                Pack<T>::unpack(ld_stream(xr + c0), x + j * NV);
+            } else {
+#pragma unroll
+                for (int e = 0; e < NV; ++e) x[j * NV + e] = fill;
+            }
+        } else {
+#pragma unroll
+            for (int e = 0; e < NV; ++e) x[j * NV + e] = (c0 + e < a.cols) ? to_f32(xr[c0 + e]) : fill;
+        }
+    }
+
+    float s0 = 1.0f, s1 = 0.0f;  // per-op row scalars
+    if (OP == OP_SOFTMAX) {
+        float m = -INFINITY;
+#pragma unroll
+        for (int i = 0; i < V * NV; ++i) m = fmaxf(m, x[i]);
+        m = group_reduce<true>(m, tpr, red0);
+        float s = 0.0f;
+#pragma unroll
+        for (int i = 0; i < V * NV; ++i) {
+            x[i] = expf(__fsub_rn(x[i], m));
+            s += x[i];
+        }
+        s0 = group_reduce<false>(s, tpr, red1);
+    } else if (OP == OP_LAYERNORM) {
+        float s = 0.0f;
+#pragma unroll
+        for (int i = 0; i < V * NV; ++i) s += x[i];
+        const float n = (float)a.cols;
+        const float mean = __fdiv_rn(group_reduce<false>(s, tpr, red0), n);
+        float q = 0.0f;
+#pragma unroll
+        for (int j = 0; j < V; ++j) {
+            const int64_t c0 = ((int64_t)j * tpr + t) * NV;
+#pragma unroll
+            for (int e = 0; e < NV; ++e) {
+                const float d = (c0 + e < a.cols) ? __fsub_rn(x[j * NV + e], mean) : 0.0f;
+                x[j * NV + e] = d;  // keep the centred value; the output needs only x - mean
+                q = __fadd_rn(q, __fmul_rn(d, d));
+            }
+        }
+        const float var = __fdiv_rn(group_reduce<false>(q, tpr, red1), n);
+        const float rstd = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(var, a.eps)));
+        s0 = rstd;
+        s1 = mean;
+        if (live && t == 0) {
+            if (a.mean) a.mean[row] = mean;
+            if (a.rstd) a.rstd[row] = rstd;
+        }
+    } else {
+        float q = 0.0f;
+#pragma unroll
+        for (int i = 0; i < V * NV; ++i) q = __fadd_rn(q, __fmul_rn(x[i], x[i]));
+        const float ms = __fdiv_rn(group_reduce<false>(q, tpr, red0), (float)a.cols);
+        s0 = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(ms, a.eps)));
+    }
+    (void)s1;
+    if (!live) return;
+
+    const T *wr = reinterpret_cast<const T *>(a.w);
+    const T *br = reinterpret_cast<const T *>(a.b);
+#pragma unroll
+    for (int j = 0; j < V; ++j) {
+        const int64_t c0 = ((int64_t)j * tpr + t) * NV;
+        if (c0 >= a.cols) continue;
+        float wv[NV], bv[NV];
+        if (OP != OP_SOFTMAX) {
+            if (VEC) {
+                Pack<T>::unpack(__ldg(reinterpret_cast<const uint4 *>(wr + c0)), wv);
+                if (OP == OP_LAYERNORM) Pack<T>::unpack(__ldg(reinterpret_cast<const uint4 *>(br + c0)), bv);
+            } else {
+#pragma unroll
+                for (int e = 0; e < NV; ++e) {
+                    const bool ok = c0 + e < a.cols;
+                    wv[e] = ok ? to_f32(wr[c0 + e]) : 0.0f;
+                    if (OP == OP_LAYERNORM) bv[e] = ok ? to_f32(br[c0 + e]) : 0.0f;
+                }
+            }
+        }
+        float o[NV];
+#pragma unroll
+        for (int e = 0; e < NV; ++e) {
+            const float v = x[j * NV + e];
+            if (OP == OP_SOFTMAX) o[e] = __fdiv_rn(v, s0);
+            else if (OP == OP_LAYERNORM) o[e] = __fadd_rn(__fmul_rn(__fmul_rn(v, s0), wv[e]), bv[e]);
+            else o[e] = __fmul_rn(__fmul_rn(v, s0), wv[e]);
+        }
+        if (VEC) {
+            st_stream(yr + c0, Pack<T>::pack(o));
+        } else {
+#pragma unroll
+            for (int e = 0; e < NV; ++e)
+                if (c0 + e < a.cols) yr[c0 + e] = from_f32<T>(o[e]);
+        }
+    }
+}
+
+// Rows too wide for registers: one 1024-thread CTA per row, three passes through L2.
+template <bool IS_MAX> __device__ float cta_reduce(float v, float *slot) {
+    v = IS_MAX ? warp_max(v) : warp_sum(v);
+    __syncthreads();  // slot may still be read from the previous reduction
+    if ((threadIdx.x & 31) == 0) slot[threadIdx.x >> 5] = v;
+    __syncthreads();
+    float r = slot[0];
+    for (int i = 1; i < (int)(blockDim.x >> 5); ++i) r = IS_MAX ? fmaxf(r, slot[i]) : r + slot[i];
+    return r;
+}
+
+template <typename T, int OP>
+__global__ void __launch_bounds__(1024) row_kernel_wide(RowArgs a) {
+    __shared__ float red[MAX_WARPS];
+    const int64_t row = blockIdx.x;
+    const T *xr = reinterpret_cast<const T *>(a.x) + row * a.stride_x;
+    T *yr = reinterpret_cast<T *>(a.y) + row * a.stride_y;
+    const T *wr = reinterpret_cast<const T *>(a.w);
+    const T *br = reinterpret_cast<const T *>(a.b);
+    const float n = (float)a.cols;
+    if (OP == OP_SOFTMAX) {
+        float m = -INFINITY;
+        for (int64_t c = threadIdx.x; c < a.cols; c += blockDim.x) m = fmaxf(m, to_f32(xr[c]));
+        m = cta_reduce<true>(m, red);
+        float s = 0.0f;
+        for (int64_t c = threadIdx.x; c < a.cols; c += blockDim.x) s += expf(__fsub_rn(to_f32(xr[c]), m));
+        s = cta_reduce<false>(s, red);
+        for (int64_t c = threadIdx.x; c < a.cols; c += blockDim.x)
+            yr[c] = from_f32<T>(__fdiv_rn(expf(__fsub_rn(to_f32(xr[c]), m)), s));
+    } else if (OP == OP_LAYERNORM) {
+        float s = 0.0f;
+        for (int64_t c = threadIdx.x; c < a.cols; c += blockDim.x) s += to_f32(xr[c]);
+        const float mean = __fdiv_rn(cta_reduce<false>(s, red), n);
+        float q = 0.0f;
+        for (int64_t c = threadIdx.x; c < a.cols; c += blockDim.x) {
+            const float d = __fsub_rn(to_f32(xr[c]), mean);
+            q = __fadd_rn(q, __fmul_rn(d, d));
+        }
+        const float var = __fdiv_rn(cta_reduce<false>(q, red), n);
+        const float rstd = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(var, a.eps)));
+        if (threadIdx.x == 0) {
+            if (a.mean) a.mean[row] = mean;
+            if (a.rstd) a.rstd[row] = rstd;
+        }
+        for (int64_t c = threadIdx.x; c < a.cols; c += blockDim.x) {
+            const float d = __fsub_rn(to_f32(xr[c]), mean);
+            yr[c] = from_f32<T>(__fadd_rn(__fmul_rn(__fmul_rn(d, rstd), to_f32(wr[c])), to_f32(br[c])));
+        }
+    } else {
+        float q = 0.0f;
+        for (int64_t c = threadIdx.x; c < a.cols; c += blockDim.x) {
+            const float v = to_f32(xr[c]);
+            q = __fadd_rn(q, __fmul_rn(v, v));
+        }
+        const float ms = __fdiv_rn(cta_reduce<false>(q, red), n);
+        const float rstd = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(ms, a.eps)));
+        for (int64_t c = threadIdx.x; c < a.cols; c += blockDim.x)
+            yr[c] = from_f32<T>(__fmul_rn(__fmul_rn(to_f32(xr[c]), rstd), to_f32(wr[c])));
+    }
+}
+
+// variant v: threads-per-row = base << (v / 3), CTA threads = {128, 256, 512}[v % 3]
+constexpr int ROW_VARIANTS = 9;
+
+template <typename T, int OP, bool VEC>
+int launch_v(const RowArgs &a, int v, int cta, cudaStream_t st) {
+    const unsigned grid = (unsigned)cdiv(a.rows, cta / a.tpr);
+    switch (v) {
+        case 1: row_kernel<T, 1, VEC, OP><<<grid, cta, 0, st>>>(a); break;
+        case 2: row_kernel<T, 2, VEC, OP><<<grid, cta, 0, st>>>(a); break;
+        case 4: row_kernel<T, 4, VEC, OP><<<grid, cta, 0, st>>>(a); break;
+        case 8:
+            if constexpr (sizeof(T) == 4) {
+                row_kernel<T, 8, VEC, OP><<<grid, cta, 0, st>>>(a);
+                break;
+            }
+            [[fallthrough]];
+        default: return fail(ENC_ERR_UNSUPPORTED, "row kernel: no instantiation for %d vectors per thread", v);
+    }
+    return ENC_OK;
+}
+
+template <typename T, int OP>
+int launch_rows(RowArgs a, int variant, cudaStream_t st, const char *name) {
+    constexpr int NV = Pack<T>::N;
+    constexpr int MAXV = 32 / NV;  // at most 32 float registers of row data per thread
+    if (a.rows == 0 || a.cols == 0) return ENC_OK;
+    if (a.rows > 0x7fffffffLL) return fail(ENC_ERR_UNSUPPORTED, "%s: more than 2^31-1 rows", name);
+    if (variant >= ROW_VARIANTS) return fail(ENC_ERR_BAD_ARG, "%s: variant %d out of range", name, variant);
+    const int shift = variant < 0 ? 0 : variant / 3;
+    int cta = variant < 0 ? 128 : (128 << (variant % 3));
+    int64_t tpr64 = next_pow2(cdiv(a.cols, (int64_t)NV * MAXV));
+    if (tpr64 < 32) tpr64 = 32;
+    tpr64 <<= shift;
+    if (tpr64 > 512) {
+        if (tpr64 >> shift > 512) {  // does not fit in registers even at 512 threads per row
+            row_kernel_wide<T, OP><<<(unsigned)a.rows, 1024, 0, st>>>(a);
+            return check_launch(name);
+        }
+        tpr64 = 512;
+    }
+    a.tpr = (int)tpr64;
+    if (cta < a.tpr) cta = a.tpr;
+    int v = next_pow2(cdiv(a.cols, (int64_t)a.tpr * NV));
+    const bool vec = a.cols % NV == 0 && a.stride_x % NV == 0 && a.stride_y % NV == 0 &&
+                     aligned16(a.x) && aligned16(a.y) &&
+                     (OP == OP_SOFTMAX || aligned16(a.w)) && (OP != OP_LAYERNORM || aligned16(a.b));
+    int rc = vec ? launch_v<T, OP, true>(a, v, cta, st) : launch_v<T, OP, false>(a, v, cta, st);
+    if (rc != ENC_OK) return rc;
+    return check_launch(name);
+}
+
+template <int OP> int dispatch(const RowArgs &a, int dtype, int variant, void *stream, const char *name) {
+    if (!a.x || !a.y) return fail(ENC_ERR_BAD_ARG, "%s: NULL input or output", name);
+    if (a.rows < 0 || a.cols < 0) return fail(ENC_ERR_BAD_ARG, "%s: negative shape", name);
+    if (a.stride_x < a.cols && a.rows > 1) return fail(ENC_ERR_BAD_ARG, "%s: row stride %lld is smaller than the row length %lld", name, (long long)a.stride_x, (long long)a.cols);
+    switch (dtype) {
+        case ENC_F32: return launch_rows<float, OP>(a, variant, as_stream(stream), name);
+        case ENC_F16: return launch_rows<__half, OP>(a, variant, as_stream(stream), name);
+        case ENC_BF16: return launch_rows<__nv_bfloat16, OP>(a, variant, as_stream(stream), name);
+        default: return fail(ENC_ERR_BAD_ARG, "%s: dtype %d is not float32, float16 or bfloat16", name, dtype);
+    }
+}
+
+}  // namespace
+
+int row_variants() { return ROW_VARIANTS; }
+void row_variant_info(int v, char *out, size_t n) {
+    snprintf(out, n, "threads_per_row=base*%d cta_threads=%d (base = row length / 32 values per thread, min 32)",
+             1 << (v / 3), 128 << (v % 3));
+}
+
+}  // namespace enc
+
+extern "C" int enc_softmax(const void *in, void *out, int64_t rows, int64_t cols, int64_t stride_in,
+                           int64_t stride_out, int dtype, int variant, void *stream) {
+    ENC_PROLOGUE();
+    enc::RowArgs a{in, out, nullptr, nullptr, nullptr, nullptr, rows, cols, stride_in, stride_out, 0.f, 32};
+    return enc::dispatch<enc::OP_SOFTMAX>(a, dtype, variant, stream, "enc_softmax");
+}
+
+extern "C" int enc_layernorm(const void *x, void *y, const void *w, const void *b, float *mean,
+                             float *rstd, int64_t rows, int64_t cols, int64_t stride_x,
+                             int64_t stride_y, float eps, int dtype, int variant, void *stream) {
+    ENC_PROLOGUE();
+    if (!w || !b) return enc::fail(ENC_ERR_BAD_ARG, "enc_layernorm: NULL weight or bias");
+    enc::RowArgs a{x, y, w, b, mean, rstd, rows, cols, stride_x, stride_y, eps, 32};
+    return enc::dispatch<enc::OP_LAYERNORM>(a, dtype, variant, stream, "enc_layernorm");
+}
+
+extern "C" int enc_rmsnorm(const void *x, const void *w, void *y, int64_t rows, int64_t cols,
+                           int64_t stride_x, int64_t stride_y, float eps, int dtype, int variant,
+                           void *stream) {
+    ENC_PROLOGUE();
+    if (!w) return enc::fail(ENC_ERR_BAD_ARG, "enc_rmsnorm: NULL weight");
+    enc::RowArgs a{x, y, w, nullptr, nullptr, nullptr, rows, cols, stride_x, stride_y, eps, 32};
+    return enc::dispatch<enc::OP_RMSNORM>(a, dtype, variant, stream, "enc_rmsnorm");
+}

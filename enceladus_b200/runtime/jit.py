@@ -1,0 +1,218 @@
+"""`@jit` kernels and the `kernel[grid](...)` launch path.
+
+Keeps the launch contract of the reference's `JITFunction` (src/enceladus/runtime/jit.py:214-418):
+the signature splits into runtime and `tl.constexpr` parameters, `kernel[grid](*args, **meta)` binds
+them, `grid` is a tuple of 1 to 3 ints or a callable of the argument dict, the launch options
+`num_warps / num_stages / dot_warps / dot_backend` are accepted, a zero in the grid is a silent no-op.
+
+What changes is what a launch does.  The reference compiles the Python body to Metal; here the body is
+never run.  The kernel's name and parameter list select an adapter in `registry.py`, which recovers the
+problem from the launch arguments exactly as the reference's host wrappers pass them and makes one call
+into the CUDA library.  A kernel that is not in the registry raises: there is no code generator, no
+interpreter and no CPU fallback in this build.
+"""
+
+from __future__ import annotations
+
+import functools
+import inspect
+import os
+from collections.abc import Callable, Iterable, Mapping
+from dataclasses import dataclass
+from typing import Any
+
+import numpy as np
+
+from enceladus_b200 import language as tl
+from enceladus_b200.runtime import interop
+
+MAX_GRID = (2**31 - 1, 65535, 65535)
+_LAUNCH_OPTIONS = ("num_warps", "num_stages", "dot_warps", "dot_backend")
+
+
+def cdiv(x: int, div: int) -> int:
+    """Returns `ceil(x / div)` for positive integers: the number of blocks that cover `x`."""
+    return -(-x // div)
+
+
+def next_power_of_2(n: int) -> int:
+    """Returns the smallest power of two that's greater than or equal to `n`."""
+    return 1 if n <= 1 else 1 << (int(n) - 1).bit_length()
+
+
+_GRID_RANK_MSG = "the grid needs 1 to 3 dimensions, but got {}. Pass a tuple such as `(n,)` or `(m, n)`."
+
+
+def resolve_grid(grid: Any, bound: Mapping[str, Any]) -> tuple[int, int, int]:
+    """Grid tuple from a tuple/int or a callable of the argument dict (jit.py:669-678)."""
+    g = grid(dict(bound)) if callable(grid) else grid
+    if isinstance(g, (int, np.integer)):
+        g = (g,)
+    g = tuple(int(x) for x in g)
+    if not 1 <= len(g) <= 3:
+        raise ValueError(_GRID_RANK_MSG.format(g))
+    if any(x < 0 for x in g):
+        raise ValueError(f"grid dimensions can't be negative, but got {g}")
+    g = (*g, *(1,) * (3 - len(g)))
+    for i, (x, lim) in enumerate(zip(g, MAX_GRID)):
+        if x > lim:
+            raise ValueError(f"grid dimension {i} is {x}, but the limit is {lim}")
+    return g  # type: ignore[return-value]
+
+
+@dataclass
+class KernelParam:
+    name: str
+    index: int
+    is_constexpr: bool
+    default: Any
+    do_not_specialize: bool
+
+
+class JITFunction:
+    """A kernel created by `@enceladus_b200.jit`.
+
+    Launch it with `kernel[grid](*args, **constexprs, num_warps=4)`.
+    """
+
+    _is_enceladus_jit = True
+
+    def __init__(self, fn: Callable[..., Any], *, interpret: bool | None = None,
+                 do_not_specialize: Iterable[str | int] = (), math_mode: str = "relaxed") -> None:
+        if not inspect.isfunction(fn):
+            raise TypeError(f"@enceladus.jit needs a function, but got {type(fn).__name__}")
+        if math_mode not in ("relaxed", "fast"):
+            raise ValueError(f"math_mode must be one of ('relaxed', 'fast'), but got {math_mode!r}")
+        self.fn = fn
+        functools.update_wrapper(self, fn)
+        self.interpret = interpret
+        self.math_mode = math_mode
+        self.signature = inspect.signature(fn)
+        names = list(self.signature.parameters)
+        dns: set[str] = set()
+        for d in do_not_specialize:
+            if isinstance(d, int):
+                if not 0 <= d < len(names):
+                    raise ValueError(f"do_not_specialize index {d} is out of range")
+                d = names[d]
+            if d not in names:
+                raise ValueError(f"do_not_specialize names unknown parameter {d!r}")
+            dns.add(d)
+        params = []
+        for i, (n, p) in enumerate(self.signature.parameters.items()):
+            if p.kind in (p.VAR_POSITIONAL, p.VAR_KEYWORD):
+                raise TypeError(f"kernel `{fn.__name__}` can't take *args or **kwargs. List every "
+                                "parameter by name.")
+            params.append(KernelParam(n, i, tl.is_constexpr_annotation(p.annotation), p.default, n in dns))
+        self.params: list[KernelParam] = params
+        self.arg_names = names
+        self._adapter = None
+        self.variant: int | None = None  # forced tile variant (None = the library's choice)
+        self.last_launch: dict[str, Any] = {}
+
+    def __repr__(self) -> str:
+        return f"JITFunction({self.__module__}:{self.__qualname__})"
+
+    def __call__(self, *args: Any, **kwargs: Any) -> Any:
+        raise RuntimeError(f"`{self.__name__}` is a @enceladus.jit function. Launch it with "
+                           f"`{self.__name__}[grid](...)`.")
+
+    def __getitem__(self, grid: Any) -> Callable[..., None]:
+        return lambda *args, **kwargs: self.run(*args, grid=grid, **kwargs)
+
+    def bind(self, args: tuple[Any, ...], kwargs: Mapping[str, Any]) -> dict[str, Any]:
+        """Binds launch arguments to parameter names, applying defaults."""
+        try:
+            ba = self.signature.bind(*args, **kwargs)
+        except TypeError as e:
+            raise TypeError(f"{self.__name__}: {e}") from None
+        ba.apply_defaults()
+        return dict(ba.arguments)
+
+    def adapter(self):
+        """The registry entry that implements this kernel; raises if there is none."""
+        if self._adapter is None:
+            from enceladus_b200.runtime import registry
+
+            self._adapter = registry.lookup(self.__name__, tuple(self.arg_names))
+        return self._adapter
+
+    def run(self, *args: Any, grid: Any, num_warps: int = 4, num_stages: int | None = None,
+            dot_warps: tuple[int, int] | None = None, dot_backend: str = "auto",
+            variant: int | None = None, **kwargs: Any) -> None:
+        """Launches the kernel.
+
+        `num_warps`, `num_stages`, `dot_warps` and `dot_backend` are accepted because the reference's
+        host wrappers pass them (examples/07_matmul_fused.py:46-47, examples/08_flash_attention.py:101-103);
+        they describe Apple SIMD-group layouts and do not affect the CUDA kernels.  `variant` picks one
+        of the hand-written tile variants of the kernel (the autotuner uses it).
+        """
+        interpret = self.interpret
+        if interpret is None:
+            interpret = os.environ.get("ENCELADUS_INTERPRET", "0") not in ("", "0")
+        if interpret:
+            raise RuntimeError(
+                "ENCELADUS_INTERPRET / interpret=True asks for the reference's CPU interpreter, which "
+                "is not part of this build: launches always run the CUDA kernels.")
+        if num_warps not in (1, 2, 4, 8, 16, 32):
+            raise ValueError(f"num_warps must be a power of two from 1 to 32, but got {num_warps}")
+        if dot_backend not in ("auto", "simdgroup", "mpp"):
+            raise ValueError(f"dot_backend must be 'auto', 'simdgroup', or 'mpp', not {dot_backend!r}")
+        bound = self.bind(args, kwargs)
+        for p in self.params:
+            if p.is_constexpr:
+                bound[p.name] = tl.unwrap(bound[p.name])
+            elif bound[p.name] is inspect.Parameter.empty:
+                raise TypeError(f"{self.__name__}: missing argument `{p.name}`")
+        g = resolve_grid(grid, bound)
+        if g[0] == 0 or g[1] == 0 or g[2] == 0:
+            return  # src/enceladus/runtime/launcher.py:459-460
+        ad = self.adapter()
+        v = self.variant if variant is None else variant
+        launch(ad, bound, g, -1 if v is None else int(v), self)
+
+
+def launch(ad, bound: dict[str, Any], grid: tuple[int, int, int], variant: int, jf: JITFunction | None) -> None:
+    """Resolves array arguments to device memory, calls the adapter, writes NumPy outputs back."""
+    staged = interop.Staged()
+    resolved = dict(bound)
+    any_numpy = False
+    extents = ad.extents(bound, grid) if ad.extents is not None else {}
+    for name, v in bound.items():
+        if isinstance(v, np.ndarray):
+            any_numpy = True
+            dense = v.flags.c_contiguous and extents.get(name) == v.size
+            resolved[name] = staged.to_device(name, v, name in ad.outputs, overwritten=dense)
+        elif interop.is_torch(v):
+            if v.device.type != "cuda":
+                raise TypeError(f"argument `{name}` is a torch tensor on {v.device}; pass a CUDA tensor "
+                                "or a NumPy array")
+        elif name in ad.arrays:
+            raise TypeError(f"argument `{name}` must be a NumPy array or a torch CUDA tensor, not "
+                            f"{type(v).__name__}")
+    torch = interop._torch()
+    dev = next((resolved[n].device for n in ad.arrays if interop.is_torch(resolved.get(n))), None)
+    ctx = torch.cuda.device(dev) if dev is not None else _null()
+    with ctx:
+        ad.launch(resolved, grid, variant, interop.current_stream())
+        if any_numpy:
+            staged.finish()
+    if jf is not None:
+        jf.last_launch = {"h2d_bytes": staged.h2d_bytes, "d2h_bytes": staged.d2h_bytes, "variant": variant}
+
+
+class _null:
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *a):
+        return False
+
+
+def jit(fn: Callable[..., Any] | None = None, *, interpret: bool | None = None,
+        do_not_specialize: Iterable[str | int] = (), math_mode: str = "relaxed"):
+    """Decorator that turns a kernel definition into a launchable `JITFunction` (jit.py:1237-1264)."""
+    if fn is not None:
+        return JITFunction(fn, interpret=interpret, do_not_specialize=do_not_specialize, math_mode=math_mode)
+    return lambda f: JITFunction(f, interpret=interpret, do_not_specialize=do_not_specialize,
+                                 math_mode=math_mode)

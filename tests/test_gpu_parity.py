@@ -1,0 +1,342 @@
+"""Parity of the CUDA kernels with the oracle and with the reference-interpreter golden vectors.
+
+Every launch goes through the public launch path (`kernel[grid](...)` -> registry -> ctypes -> C ABI).
+Integer results must be bit-exact; float results use the reference's own differential-test tolerances
+(tests/conftest.py:75-79 of the reference): fp32 (1e-5, 1e-5), fp16 (1e-3, 2e-3), bf16 (1e-2, 1.6e-2).
+"""
+
+from __future__ import annotations
+
+import numpy as np
+import pytest
+from conftest import BF16, F16, F32, assert_close, load_golden
+
+import enceladus_b200 as enceladus
+from enceladus_b200 import _native as N
+from enceladus_b200 import ops
+from enceladus_b200.workloads import zipf_clipped
+
+pytestmark = pytest.mark.gpu
+
+
+def torch_of(a: np.ndarray):
+    import torch
+
+    from enceladus_b200.runtime import interop
+
+    return interop._np_as_torch_view(np.ascontiguousarray(a)).to("cuda")
+
+
+def host(t) -> np.ndarray:
+    from enceladus_b200.testing import _host
+
+    return _host(t)
+
+
+def randn(rng, shape, dt):
+    return rng.standard_normal(shape).astype(np.float32).astype(dt)
+
+
+# ---- softmax ---------------------------------------------------------------------------------------
+def test_softmax_golden():
+    g = load_golden("softmax")
+    for k in [k[:-2] for k in g if k.endswith("_x")]:
+        assert_close(ops.softmax(g[k + "_x"]), g[k + "_y"], what=k)  # NumPy arguments: staged and copied back
+
+
+def test_softmax_config1(oracle):
+    x = np.random.default_rng(0).standard_normal((4096, 1024)).astype(np.float32) * 4
+    want = oracle.softmax(x)
+    got = host(ops.softmax(torch_of(x)))
+    assert_close(got, want)
+    assert_close(got[:8], load_golden("softmax")["config1_rows0_8"])
+    np.testing.assert_allclose(got.sum(axis=1, dtype=np.float64), 1.0, atol=1e-5)
+
+
+@pytest.mark.parametrize("dt", [F32, F16, BF16], ids=str)
+@pytest.mark.parametrize("shape", [(1, 1), (5, 33), (64, 4096), (33, 5000), (3, 40_000), (2, 65_536)])
+def test_softmax_shapes(oracle, dt, shape):
+    x = randn(np.random.default_rng(shape[1]), shape, dt) * dt.type(4)
+    assert_close(host(ops.softmax(torch_of(x))), oracle.softmax(x))
+
+
+def test_softmax_strided_rows_and_offset_views(oracle):
+    import torch
+
+    x = randn(np.random.default_rng(1), (16, 1024), F32)
+    big = torch_of(x)
+    view = big[2:11, 4:1004]  # row stride 1024, 16-byte aligned start but ragged length
+    assert_close(host(ops.softmax(view)), oracle.softmax(x[2:11, 4:1004]))
+    odd = big[:, 1:1001]  # misaligned start: scalar path
+    assert_close(host(ops.softmax(odd)), oracle.softmax(x[:, 1:1001]))
+    full = torch.full((9, 2048), 7.0, device="cuda")
+    out = full[:, :1000]  # strided output: the gaps between rows must stay untouched
+    ops.softmax_kernel[(9,)](out, view, 1024, 2048, 1000, BLOCK=1024)
+    assert_close(host(out), oracle.softmax(x[2:11, 4:1004]))
+    assert float(full[:, 1000:].min()) == 7.0 and float(full[:, 1000:].max()) == 7.0
+
+
+def test_softmax_every_variant(oracle):
+    x = randn(np.random.default_rng(2), (300, 2048), F16)
+    want = oracle.softmax(x)
+    xt = torch_of(x)
+    for v in range(N.num_variants(N.K_SOFTMAX)):
+        out = enceladus.new_empty(xt)
+        ops.softmax_kernel[(300,)](out, xt, 2048, 2048, 2048, BLOCK=2048, variant=v)
+        assert_close(host(out), want, what=f"variant {v}")
+
+
+# ---- layernorm / rmsnorm ---------------------------------------------------------------------------
+def test_layernorm_golden():
+    g = load_golden("layernorm")
+    for k in [k[:-2] for k in g if k.endswith("_x")]:
+        block = int(k.rsplit("_b", 1)[1])
+        y, mean, rstd = ops.layernorm(g[k + "_x"], g[k + "_w"], g[k + "_b"], 1e-5, block)
+        assert_close(y, g[k + "_y"], atol=1e-4 if y.dtype == F32 else None, what=k)
+        assert_close(mean, g[k + "_mean"], atol=1e-5, rtol=1e-5)
+        assert_close(rstd, g[k + "_rstd"], atol=1e-5, rtol=1e-5)
+
+
+@pytest.mark.parametrize("dt,shape", [(BF16, (2048, 4096)), (F16, (7, 1000)), (F32, (64, 8192)), (BF16, (3, 20_000)),
+                                      (F32, (2, 33_000)), (BF16, (5, 17))], ids=str)
+def test_layernorm_shapes(oracle, dt, shape):
+    r = np.random.default_rng(shape[0])
+    x = randn(r, shape, dt)
+    w = (1 + 0.1 * r.standard_normal(shape[1])).astype(np.float32).astype(dt)
+    b = (0.1 * r.standard_normal(shape[1])).astype(np.float32).astype(dt)
+    y, mean, rstd = ops.layernorm(torch_of(x), torch_of(w), torch_of(b))
+    wy, wm, wr = oracle.layernorm(x, w, b)
+    assert_close(host(y), wy, atol=1e-4 if dt == F32 else None)
+    assert_close(host(mean), wm, atol=1e-5, rtol=1e-5)
+    assert_close(host(rstd), wr, atol=1e-5, rtol=1e-5)
+
+
+def test_rmsnorm_golden():
+    g = load_golden("rmsnorm")
+    for k in [k[:-2] for k in g if k.endswith("_x")]:
+        assert_close(ops.rmsnorm(g[k + "_x"], g[k + "_w"], 1e-6), g[k + "_y"], what=k)
+
+
+@pytest.mark.parametrize("dt,shape", [(BF16, (2048, 4096)), (F16, (9, 1000)), (F32, (4, 128)), (BF16, (3, 40_000))],
+                         ids=str)
+def test_rmsnorm_shapes(oracle, dt, shape):
+    r = np.random.default_rng(shape[1])
+    x, w = randn(r, shape, dt), (1 + 0.1 * r.standard_normal(shape[1])).astype(np.float32).astype(dt)
+    assert_close(host(ops.rmsnorm(torch_of(x), torch_of(w))), oracle.rmsnorm(x, w))
+
+
+def test_norm_variants(oracle):
+    r = np.random.default_rng(3)
+    x, w, b = randn(r, (100, 4096), BF16), randn(r, 4096, BF16), randn(r, 4096, BF16)
+    wy, _, _ = oracle.layernorm(x, w, b)
+    wr = oracle.rmsnorm(x, w)
+    xt, wt, bt = torch_of(x), torch_of(w), torch_of(b)
+    import torch
+
+    for v in range(N.num_variants(N.K_LAYERNORM)):
+        y = enceladus.new_empty(xt)
+        mean = torch.empty(100, device="cuda")
+        rstd = torch.empty(100, device="cuda")
+        ops.layernorm_kernel[(100,)](xt, y, wt, bt, mean, rstd, 4096, 4096, 4096, 1e-5, BLOCK=1024, variant=v)
+        assert_close(host(y), wy, what=f"layernorm variant {v}")
+        o = enceladus.new_empty(xt)
+        ops.rmsnorm_kernel[(100,)](xt, wt, o, 4096, 4096, 4096, 1e-6, BLOCK=4096, variant=v)
+        assert_close(host(o), wr, what=f"rmsnorm variant {v}")
+
+
+# ---- GELU ------------------------------------------------------------------------------------------
+def test_gelu_golden():
+    g = load_golden("gelu")
+    for k in [k[:-2] for k in g if k.endswith("_x") and not k.startswith("tanh")]:
+        assert_close(ops.fused_gelu(g[k + "_x"], g[k + "_bias"], 0.75), g[k + "_y"], what=k)
+    assert_close(ops.tanh_gelu(g["tanh_f32_x"]), g["tanh_f32_y"])
+
+
+@pytest.mark.parametrize("n", [1, 3, 1023, (1 << 20) + 3])
+def test_tanh_gelu_sizes_and_variants(oracle, n):
+    x = (np.random.default_rng(n).standard_normal(n) * 2).astype(np.float32)
+    want = oracle.gelu_tanh(x)
+    xt = torch_of(x)
+    for v in [None, *range(N.num_variants(N.K_GELU))]:
+        out = enceladus.new_empty(xt)
+        ops.tanh_gelu_kernel[(enceladus.cdiv(n, 1024),)](xt, out, n, BLOCK=1024, variant=v)
+        assert_close(host(out), want, what=f"variant {v}")
+
+
+def test_fused_gelu_ragged_columns_and_misaligned_base(oracle):
+    r = np.random.default_rng(4)
+    x, bias = randn(r, (257, 301), BF16), randn(r, 301, BF16)
+    assert_close(host(ops.fused_gelu(torch_of(x), torch_of(bias), 1.5)), oracle.fused_gelu(x, bias, 1.5))
+    flat = torch_of(randn(r, 4099, F32))
+    xs = flat[3:]  # 12-byte offset
+    out = enceladus.new_empty(xs)
+    ops.tanh_gelu_kernel[(5,)](xs, out, 4096, BLOCK=1024)
+    assert_close(host(out), oracle.gelu_tanh(host(xs)))
+
+
+def test_add(oracle):
+    r = np.random.default_rng(5)
+    for dt in (F32, F16, BF16):
+        for n in (1, 1000, (1 << 16) + 3):
+            x, y = randn(r, n, dt), randn(r, n, dt)
+            assert_close(host(ops.add(torch_of(x), torch_of(y))), oracle.vector_add(x, y))
+
+
+# ---- histogram -------------------------------------------------------------------------------------
+def test_histogram_golden():
+    g = load_golden("histogram")
+    x = np.random.default_rng(5).standard_normal(100_003).astype(np.float32)
+    np.testing.assert_array_equal(ops.histogram(x, 48, -3.0, 3.0), g["f32_100003_48bins"])
+    x = np.random.default_rng(0).integers(0, 256, 1 << 18).astype(np.int32)
+    np.testing.assert_array_equal(ops.histogram(x, 256, 0.0, 256.0), g["i32_uniform256_2p18"])
+    x = zipf_clipped(np.random.default_rng(1), 1 << 16, 1.1, 4096)
+    np.testing.assert_array_equal(ops.histogram(x, 4096, 0.0, 4096.0), g["i32_zipf4096_2p16"])
+
+
+def test_histogram_int32_every_variant(oracle):
+    n = (1 << 24) + 5
+    u = np.random.default_rng(0).integers(0, 256, n).astype(np.int32)
+    z = zipf_clipped(np.random.default_rng(1), n, 1.1, 4096)
+    wu, wz = oracle.histogram(u, 256, 0.0, 256.0), oracle.histogram(z, 4096, 0.0, 4096.0)
+    ut, zt = torch_of(u), torch_of(z)
+    for v in range(N.num_variants(N.K_HISTOGRAM)):
+        for xt, bins, want in ((ut, 256, wu), (zt, 4096, wz)):
+            hist = enceladus.new_zeros(xt, (bins,), np.int32)
+            ops.histogram_kernel[(enceladus.cdiv(n, 1024),)](xt, hist, n, 0.0, 1.0, NUM_BINS=bins, BLOCK=1024,
+                                                             variant=v)
+            np.testing.assert_array_equal(host(hist), want, err_msg=f"variant {v} bins {bins}")
+
+
+def test_histogram_drops_out_of_range_nan_and_accumulates(oracle):
+    x = np.array([-1.0, 0.0, 0.5, 3.999, 4.0, np.nan, np.inf, -np.inf, 1e30, 2.0], np.float32)
+    want = oracle.histogram(x, 4, 0.0, 4.0)
+    np.testing.assert_array_equal(ops.histogram(x, 4, 0.0, 4.0), want)
+    big = np.array([-5, 0, 3, 4, 2**31 - 1, -(2**31), 2], np.int32)
+    np.testing.assert_array_equal(ops.histogram(big, 4, 0.0, 4.0), oracle.histogram(big, 4, 0.0, 4.0))
+    xt = torch_of(x)
+    hist = enceladus.new_zeros(xt, (4,), np.int32)
+    for _ in range(2):  # atomic_add semantics: a second launch adds to the first
+        ops.histogram_kernel[(1,)](xt, hist, x.size, 0.0, 1.0, NUM_BINS=4, BLOCK=1024)
+    np.testing.assert_array_equal(host(hist), 2 * want)
+
+
+def test_histogram_misaligned_halfs_and_many_bins(oracle):
+    r = np.random.default_rng(6)
+    x = randn(r, 100_001, F16)
+    xt = torch_of(x)[1:]
+    np.testing.assert_array_equal(host(ops.histogram(xt, 64, -4.0, 4.0)), oracle.histogram(x[1:], 64, -4.0, 4.0))
+    xb = randn(r, 50_000, BF16)
+    np.testing.assert_array_equal(host(ops.histogram(torch_of(xb), 33, -2.0, 2.0)), oracle.histogram(xb, 33, -2.0, 2.0))
+    big = r.integers(0, 100_000, 1 << 20).astype(np.int32)  # more bins than shared memory holds
+    np.testing.assert_array_equal(host(ops.histogram(torch_of(big), 100_000, 0.0, 100_000.0)),
+                                  oracle.histogram(big, 100_000, 0.0, 100_000.0))
+
+
+# ---- cumsum ----------------------------------------------------------------------------------------
+def test_cumsum_golden():
+    from test_oracle_golden import cumsum_input
+
+    g = load_golden("cumsum")
+    for k in g:
+        if "_rev" not in k:
+            continue
+        name, shape, rev = k.split("_")
+        shape = tuple(int(s) for s in shape.split("x"))
+        got = ops.cumsum(cumsum_input(name, shape), reverse=bool(int(rev[-1])))
+        assert_close(got, g[k], atol=1e-4 if got.dtype == F32 else None, rtol=1e-4 if got.dtype == F32 else None, what=k)
+    x = np.random.default_rng(9).integers(0, 1 << 20, (2, 65536)).astype(np.int32)
+    np.testing.assert_array_equal(ops.cumsum(x)[:, -16:], g["i32_wrap_2x65536_tail"])
+
+
+@pytest.mark.parametrize("n", [1, 7, 4096, 4097, 12_345, (1 << 24) + 13])
+def test_flat_cumsum_int32_bit_exact(oracle, n):
+    x = np.random.default_rng(n).integers(0, 1 << 28, n).astype(np.int32)  # wraps after ~16 elements
+    want = oracle.cumsum(x)
+    xt = torch_of(x)
+    for v in [None, *range(N.num_variants(N.K_CUMSUM))]:
+        out = enceladus.new_empty(xt)
+        ops.cumsum_kernel[(1,)](out, xt, 1, n, n, n, REVERSE=False, BLOCK_M=1, BLOCK_N=enceladus.next_power_of_2(n),
+                                variant=v)
+        np.testing.assert_array_equal(host(out), want, err_msg=f"variant {v}")
+    enceladus.synchronize()  # raises if a look-back wait ran out
+
+
+def test_flat_cumsum_float32_tolerance(oracle):
+    n = 1 << 24
+    x = np.random.default_rng(0).standard_normal(n).astype(np.float32)
+    exact = np.cumsum(x.astype(np.float64))
+    ref_err = np.abs(oracle.cumsum(x).astype(np.float64) - exact).max()
+    got = host(ops.cumsum(torch_of(x))).astype(np.float64)
+    # no worse than the reference's own sequential float32 accumulation, floor 1e-4 of the range
+    assert np.abs(got - exact).max() <= max(ref_err, 1e-4 * np.abs(exact).max())
+
+
+def test_flat_cumsum_misaligned_and_other_dtypes(oracle):
+    r = np.random.default_rng(7)
+    x = r.integers(-100, 100, 50_001).astype(np.int32)
+    xt = torch_of(x)[1:]
+    np.testing.assert_array_equal(host(ops.cumsum(xt)), oracle.cumsum(x[1:]))
+    for dt in (np.int8, np.int16, np.uint8, np.int64):
+        v = r.integers(0, 100, 30_000).astype(dt)
+        got = host(ops.cumsum(torch_of(v)))
+        want = oracle.cumsum(v)
+        np.testing.assert_array_equal(got, want.astype(got.dtype))
+    for dt in (F16, BF16):
+        v = randn(r, 20_000, dt)
+        assert_close(host(ops.cumsum(torch_of(v))), oracle.cumsum(v), atol=0.5, rtol=2e-2)
+
+
+def test_row_cumsum_shapes(oracle):
+    r = np.random.default_rng(8)
+    for shape in ((4096, 512), (3, 70_000), (1000, 7)):
+        x = r.integers(-1000, 1000, shape).astype(np.int32)
+        for rev in (False, True):
+            np.testing.assert_array_equal(host(ops.cumsum(torch_of(x), reverse=rev)), oracle.cumsum(x, rev))
+    import torch
+
+    x = r.standard_normal((64, 1024)).astype(np.float32)
+    view = torch_of(x)[:, 8:1000]  # strided rows
+    assert_close(host(ops.cumsum(view)), oracle.cumsum(x[:, 8:1000]), atol=1e-3, rtol=1e-4)
+    assert isinstance(view, torch.Tensor)
+
+
+def test_sharded_flat_cumsum_matches_single_pass(oracle):
+    """The multi-GPU recipe (local total -> offset -> seeded scan) on one device, shard by shard."""
+    import torch
+
+    from enceladus_b200 import dist as edist
+
+    n, world = 1_000_003, 4
+    x = np.random.default_rng(11).integers(0, 1 << 29, n).astype(np.int32)
+    want = oracle.cumsum(x)
+    shards = [torch_of(x[slice(*edist.shard_range(n, r, world, 4))]) for r in range(world)]
+    totals = np.concatenate([host(edist.cuda_total(s)) for s in shards])
+    offs = edist.exclusive_offsets(totals)
+    got = np.concatenate([host(edist.cuda_scan(s, torch.from_numpy(offs[r : r + 1].copy()).cuda()))
+                          for r, s in enumerate(shards)])
+    np.testing.assert_array_equal(got, want)
+
+
+# ---- launch path -----------------------------------------------------------------------------------
+def test_numpy_arguments_are_written_back_and_async_numpy_defers(oracle):
+    x = np.random.default_rng(12).standard_normal((8, 256)).astype(np.float32)
+    out = np.zeros_like(x)
+    with enceladus.async_numpy(True):
+        ops.softmax_kernel[(8,)](out, x, 256, 256, 256, BLOCK=256)
+        enceladus.synchronize()
+    assert_close(out, oracle.softmax(x))
+    assert ops.softmax_kernel.last_launch["h2d_bytes"] == x.nbytes  # the dense output is not copied in
+
+
+def test_injected_failure_surfaces_as_cuda_error():
+    x = torch_of(np.zeros((2, 8), np.float32))
+    N.load().enc_test_fail_next(N.ERR_LAUNCH)
+    with pytest.raises(enceladus.CudaError, match="injected"):
+        ops.softmax(x)
+    ops.softmax(x)  # the next launch is unaffected
+    enceladus.synchronize()
+
+
+def test_device_info_reports_blackwell():
+    info = N.device_info()
+    assert info.sm_count > 0 and info.cc_major >= 10, (info.cc_major, info.cc_minor)
