@@ -247,6 +247,7 @@ def workloads(scale: float = 1.0):
     return W
 
 
+USE_GRAPH = True
 RANK = int(os.environ.get("RANK", "0"))
 LOCAL_RANK = int(os.environ.get("LOCAL_RANK", "0"))
 WORLD = int(os.environ.get("WORLD_SIZE", "1"))
@@ -311,18 +312,33 @@ def visible_gpu_index(local_rank: int) -> int:
     return local_rank
 
 
-def timed_region(run, sets, steps: int, warmup: int):
-    """W warm-up steps, then exactly K steps between two events; returns ms per step (max over ranks)."""
+def timed_region(run, sets, steps: int, warmup: int, graph: bool = True):
+    """W warm-up steps, then exactly K steps between two events; returns ms per step (max over ranks).
+
+    The K steps are captured into one CUDA graph and replayed, so that host launch latency (a few
+    microseconds per launch through Python) does not hide kernels that run for about as long.
+    """
     import torch
 
     for i in range(warmup):
         run(sets[i % len(sets)])
+    torch.cuda.synchronize()
+    g = None
+    if graph:
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            for i in range(steps):
+                run(sets[(warmup + i) % len(sets)])
+        g.replay()  # untimed: uploads the graph
     barrier()
     torch.cuda.synchronize()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
-    for i in range(steps):
-        run(sets[(warmup + i) % len(sets)])
+    if g is not None:
+        g.replay()
+    else:
+        for i in range(steps):
+            run(sets[(warmup + i) % len(sets)])
     e1.record()
     torch.cuda.synchronize()
     barrier()
@@ -371,13 +387,14 @@ def bench_workload(wl: dict, steps: int, warmup: int, pk: dict, pk_kind: str, sa
     sets = [wl["make"](1000 * RANK + i) for i in range(nsets)]
     torch.cuda.synchronize()
     m0 = sampler.mark() if sampler else 0
-    ms = timed_region(wl["run"], sets, steps, warmup)
+    graph = USE_GRAPH and not (WORLD > 1 and wl["kernel"] in ("histogram", "cumsum"))  # collectives stay eager
+    ms = timed_region(wl["run"], sets, steps, warmup, graph)
     m1 = sampler.mark() if sampler else 0
     achieved = wl["work"] / (ms * 1e-3) / (1e9 if wl["unit"] == "GB/s" else 1e12)
     peak = pk["hbm_gbs"] if wl["bound"] == "hbm" else pk["bf16_tflops"]
     row = {
         "name": wl["name"], "value": achieved * WORLD, "unit": wl["unit"], "ms_per_step": ms, "steps": steps,
-        "warmup": warmup, "dtype": wl["dtype"], "buffer_sets": nsets,
+        "warmup": warmup, "dtype": wl["dtype"], "buffer_sets": nsets, "cuda_graph": graph,
         "roofline": {"bound": wl["bound"], "achieved": achieved, "peak": peak, "unit": wl["unit"],
                      "frac": achieved / peak, "peak_source": pk_kind, "traffic": NCU_TRAFFIC.get(wl["name"])},
     }
@@ -490,9 +507,12 @@ def main() -> None:
     ap.add_argument("--kernel-steps", type=int, default=10)
     ap.add_argument("--scale", type=float, default=1.0, help="shrinks the 2^30 / 2^28 element workloads")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-graph", action="store_true", help="launch the timed steps eagerly instead of as one CUDA graph")
     ap.add_argument("--cpu-baseline-all", action="store_true")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
+    global USE_GRAPH
+    USE_GRAPH = not args.no_graph
 
     if args.impl == "reference":
         reference_arm(args)
@@ -544,7 +564,8 @@ def main() -> None:
         "ms_per_step": head["ms_per_step"], "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": head["dtype"], "data": "synthetic",
         "config": {"workload": head["name"], "l2": f"rotating {head['buffer_sets']} buffer sets (> 4x L2 in total)",
-                   "sharding": "same per-GPU workload on every rank, no data-path collective"},
+                   "sharding": "same per-GPU workload on every rank, no data-path collective",
+                   "timed_region": "K launches captured in one CUDA graph" if head.get("cuda_graph") else "K eager launches"},
         "roofline": head["roofline"], "clocks": head.get("clocks"), "gpu_launches": launches,
         "e2e": head.get("e2e"), "cpu_baseline": head.get("cpu_baseline"), "per_kernel": rows,
     }

@@ -27,6 +27,7 @@ constexpr int QUADS = 4;                 // quads (4 consecutive elements) per t
 constexpr int ITEMS = QUADS * 4;         // elements per thread per tile
 constexpr unsigned FLAG_EMPTY = 0, FLAG_AGGREGATE = 1, FLAG_PREFIX = 2;
 constexpr unsigned SPIN_LIMIT = 1u << 20;  // polls of one descriptor before giving up
+constexpr int LOOK = 4;                    // descriptors inspected per lane per look-back round
 
 // ---- element access ------------------------------------------------------------------------
 template <typename T> struct AccOf { using type = float; };
@@ -197,36 +198,57 @@ __global__ void __launch_bounds__(THREADS) scan_lookback_kernel(FlatArgs a) {
                 if (lane == 0) desc_store(a.desc, FLAG_PREFIX, bits_of(Acc(exclusive + total)));
             } else {
                 if (lane == 0) desc_store(a.desc + tile, FLAG_AGGREGATE, bits_of(total));
-                int64_t look = tile - 1;  // lane 0 inspects the nearest predecessor
+                // Look back over 32*LOOK descriptors per round: lane l inspects the LOOK predecessors at
+                // distances l*LOOK+1 .. l*LOOK+LOOK, nearest first.  The wave of known prefixes then
+                // advances 32*LOOK tiles per L2 round trip, which keeps it ahead of the memory system.
+                int64_t look = tile - 1;
                 bool done = false;
                 while (!done) {
-                    const int64_t idx = look - lane;
-                    unsigned flag = FLAG_PREFIX, bits = 0;  // "before tile 0" acts as a zero prefix
-                    if (idx >= 0) {
-                        unsigned spins = 0;
-                        for (;;) {
+                    unsigned flag[LOOK], bits[LOOK];
+#pragma unroll
+                    for (int k = 0; k < LOOK; ++k) {
+                        const int64_t idx = look - (int64_t)lane * LOOK - k;
+                        flag[k] = FLAG_PREFIX;  // "before tile 0" acts as a zero prefix
+                        bits[k] = 0;
+                        if (idx >= 0) {
                             const unsigned long long w = desc_load(a.desc + idx);
-                            flag = (unsigned)(w >> 32);
-                            bits = (unsigned)w;
-                            if (flag != FLAG_EMPTY) break;
-                            if (++spins > SPIN_LIMIT) {  // give up: flag the error, stop waiting
-                                atomicExch(a.error, 1u);
-                                flag = FLAG_PREFIX;
-                                bits = 0;
-                                break;
-                            }
-                            __nanosleep(32);
+                            flag[k] = (unsigned)(w >> 32);
+                            bits[k] = (unsigned)w;
                         }
                     }
-                    const unsigned has_prefix = __ballot_sync(0xffffffffu, flag == FLAG_PREFIX);
-                    // lanes nearer than the first PREFIX contribute aggregates; that lane its prefix
+#pragma unroll
+                    for (int k = 0; k < LOOK; ++k) {
+                        const int64_t idx = look - (int64_t)lane * LOOK - k;
+                        unsigned spins = 0;
+                        while (flag[k] == FLAG_EMPTY) {  // the predecessor is still scanning its tile
+                            if (++spins > SPIN_LIMIT) {  // give up: flag the error, stop waiting
+                                atomicExch(a.error, 1u);
+                                flag[k] = FLAG_PREFIX;
+                                bits[k] = 0;
+                                break;
+                            }
+                            if (spins > 8) __nanosleep(20);
+                            const unsigned long long w = desc_load(a.desc + idx);
+                            flag[k] = (unsigned)(w >> 32);
+                            bits[k] = (unsigned)w;
+                        }
+                    }
+                    // my LOOK descriptors, nearest first, up to and including my first PREFIX
+                    Acc mine = 0;
+                    bool has = false;
+#pragma unroll
+                    for (int k = 0; k < LOOK; ++k) {
+                        if (!has) mine += acc_of_bits<Acc>(bits[k]);
+                        has = has || flag[k] == FLAG_PREFIX;
+                    }
+                    const unsigned has_prefix = __ballot_sync(0xffffffffu, has);
                     const int stop = has_prefix ? __ffs(has_prefix) - 1 : 31;
-                    Acc contrib = lane <= stop ? acc_of_bits<Acc>(bits) : Acc(0);
+                    Acc contrib = lane <= stop ? mine : Acc(0);
 #pragma unroll
                     for (int o = 16; o > 0; o >>= 1) contrib += __shfl_xor_sync(0xffffffffu, contrib, o);
                     exclusive += contrib;
                     done = has_prefix != 0;
-                    look -= 32;
+                    look -= 32 * LOOK;
                 }
                 if (lane == 0) desc_store(a.desc + tile, FLAG_PREFIX, bits_of(Acc(exclusive + total)));
             }
@@ -339,32 +361,47 @@ __global__ void __launch_bounds__(1024) sum_final_kernel(const Acc *partials, in
 }
 
 // ---- scratch -------------------------------------------------------------------------------
-// One buffer per (device, stream): launches on one stream are ordered, so they can share it.
+// One buffer per (device, stream): launches on one stream are ordered, so they can share it, and
+// launches on different streams never collide.  A stream that is being captured into a CUDA graph
+// cannot allocate, and the graph may later be replayed on any stream, so captured launches use one
+// extra per-device buffer that every ordinary call keeps at least as large as its own (run the
+// same call once before capturing it).
 struct Scratch { void *ptr = nullptr; size_t bytes = 0; };
 std::mutex g_scratch_mu;
 std::map<std::pair<int, void *>, Scratch> g_scratch;
+void *const kCaptureKey = reinterpret_cast<void *>(~uintptr_t(0));
+
+bool grow(Scratch &s, size_t bytes, cudaStream_t st) {
+    if (s.bytes >= bytes) return true;
+    if (s.ptr) {
+        cudaStreamSynchronize(st);  // earlier launches may still use it
+        cudaFree(s.ptr);
+    }
+    s.ptr = nullptr;
+    s.bytes = 0;
+    const size_t want = bytes < (1u << 20) ? (1u << 20) : bytes;
+    if (cudaMalloc(&s.ptr, want) != cudaSuccess) {
+        cudaGetLastError();
+        s.ptr = nullptr;
+        return false;
+    }
+    s.bytes = want;
+    return true;
+}
 
 void *scratch_get(size_t bytes, void *stream) {
     int dev = 0;
     cudaGetDevice(&dev);
+    cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+    if (cudaStreamIsCapturing(as_stream(stream), &cap) != cudaSuccess) cudaGetLastError();
     std::lock_guard<std::mutex> lock(g_scratch_mu);
-    Scratch &s = g_scratch[{dev, stream}];
-    if (s.bytes < bytes) {
-        if (s.ptr) {
-            cudaStreamSynchronize(as_stream(stream));  // earlier launches may still use it
-            cudaFree(s.ptr);
-        }
-        s.ptr = nullptr;
-        s.bytes = 0;
-        size_t want = bytes < (1u << 20) ? (1u << 20) : bytes;
-        if (cudaMalloc(&s.ptr, want) != cudaSuccess) {
-            cudaGetLastError();
-            s.ptr = nullptr;
-            return nullptr;
-        }
-        s.bytes = want;
+    if (cap != cudaStreamCaptureStatusNone) {
+        Scratch &c = g_scratch[{dev, kCaptureKey}];
+        return c.bytes >= bytes ? c.ptr : nullptr;
     }
-    return s.ptr;
+    if (!grow(g_scratch[{dev, kCaptureKey}], bytes, nullptr)) return nullptr;
+    Scratch &s = g_scratch[{dev, stream}];
+    return grow(s, bytes, as_stream(stream)) ? s.ptr : nullptr;
 }
 
 // variant v: CTA threads = {256, 512, 1024}[v]  (tile = threads * 16 elements)
@@ -378,7 +415,7 @@ int launch_flat_t(const void *in, void *out, int64_t n, const void *seed, cudaSt
     const int64_t ntiles = cdiv(n, TILE);
     const size_t bytes = 64 + (size_t)ntiles * 8;
     char *scr = (char *)scratch_get(bytes, stream);
-    if (!scr) return fail(ENC_ERR_NO_MEMORY, "enc_cumsum: cannot allocate %zu bytes of tile descriptors", bytes);
+    if (!scr) return fail(ENC_ERR_NO_MEMORY, "enc_cumsum: cannot allocate %zu bytes of tile descriptors (inside a stream capture nothing can be allocated: run the same call once before capturing)", bytes);
     unsigned *err = device_error_word();
     if (!err) return fail(ENC_ERR_NO_MEMORY, "enc_cumsum: cannot allocate the device status word");
     cudaError_t e = cudaMemsetAsync(scr, 0, bytes, st);

@@ -50,6 +50,15 @@ __device__ __forceinline__ float group_reduce(float v, int tpr, float *slot) {
     return v;
 }
 
+// A row lives in registers as V raw 16-byte vectors per thread (float16/bfloat16 stay packed, which
+// halves the register cost and lets one warp hold a 4096-wide row); every pass unpacks to float32
+// on the fly.
+template <typename T, int V> union RowRegs {
+    uint4 v[V];
+    T e[V * Pack<T>::N];
+    __device__ RowRegs() {}
+};
+
 template <typename T, int V, bool VEC, int OP>
 __global__ void __launch_bounds__(512) row_kernel(RowArgs a) {
     constexpr int NV = Pack<T>::N;
@@ -63,50 +72,75 @@ __global__ void __launch_bounds__(512) row_kernel(RowArgs a) {
     T *yr = reinterpret_cast<T *>(a.y) + (live ? row : 0) * a.stride_y;
     const float fill = OP == OP_SOFTMAX ? -INFINITY : 0.0f;
 
-    float x[V * NV];
+    RowRegs<T, V> x;
 #pragma unroll
     for (int j = 0; j < V; ++j) {
         const int64_t c0 = ((int64_t)j * tpr + t) * NV;
         if (VEC) {
+            if (c0 < a.cols) x.v[j] = ld_stream(xr + c0);
+        } else {
+#pragma unroll
+            for (int e = 0; e < NV; ++e)
+                if (c0 + e < a.cols) x.e[j * NV + e] = xr[c0 + e];
+        }
+    }
+    // value (j, e) as float, `fill` beyond the row
+    auto get = [&](int j, float *f) {
+        const int64_t c0 = ((int64_t)j * tpr + t) * NV;
+        if (VEC) {
             if (c0 < a.cols) {
-                Pack<T>::unpack(ld_stream(xr + c0), x + j * NV);
+                Pack<T>::unpack(x.v[j], f);
             } else {
 #pragma unroll
-                for (int e = 0; e < NV; ++e) x[j * NV + e] = fill;
+                for (int e = 0; e < NV; ++e) f[e] = fill;
             }
         } else {
 #pragma unroll
-            for (int e = 0; e < NV; ++e) x[j * NV + e] = (c0 + e < a.cols) ? to_f32(xr[c0 + e]) : fill;
+            for (int e = 0; e < NV; ++e) f[e] = (c0 + e < a.cols) ? to_f32(x.e[j * NV + e]) : fill;
         }
-    }
+    };
 
-    float s0 = 1.0f, s1 = 0.0f;  // per-op row scalars
+    float s0 = 1.0f, s1 = 0.0f;  // softmax: max, sum.  layernorm: rstd, mean.  rmsnorm: rstd.
     if (OP == OP_SOFTMAX) {
         float m = -INFINITY;
 #pragma unroll
-        for (int i = 0; i < V * NV; ++i) m = fmaxf(m, x[i]);
+        for (int j = 0; j < V; ++j) {
+            float f[NV];
+            get(j, f);
+#pragma unroll
+            for (int e = 0; e < NV; ++e) m = fmaxf(m, f[e]);
+        }
         m = group_reduce<true>(m, tpr, red0);
         float s = 0.0f;
 #pragma unroll
-        for (int i = 0; i < V * NV; ++i) {
-            x[i] = expf(__fsub_rn(x[i], m));
-            s += x[i];
+        for (int j = 0; j < V; ++j) {
+            float f[NV];
+            get(j, f);
+#pragma unroll
+            for (int e = 0; e < NV; ++e) s += expf(__fsub_rn(f[e], m));
         }
-        s0 = group_reduce<false>(s, tpr, red1);
+        s1 = group_reduce<false>(s, tpr, red1);
+        s0 = m;
     } else if (OP == OP_LAYERNORM) {
         float s = 0.0f;
 #pragma unroll
-        for (int i = 0; i < V * NV; ++i) s += x[i];
+        for (int j = 0; j < V; ++j) {
+            float f[NV];
+            get(j, f);
+#pragma unroll
+            for (int e = 0; e < NV; ++e) s += f[e];
+        }
         const float n = (float)a.cols;
         const float mean = __fdiv_rn(group_reduce<false>(s, tpr, red0), n);
         float q = 0.0f;
 #pragma unroll
         for (int j = 0; j < V; ++j) {
             const int64_t c0 = ((int64_t)j * tpr + t) * NV;
+            float f[NV];
+            get(j, f);
 #pragma unroll
             for (int e = 0; e < NV; ++e) {
-                const float d = (c0 + e < a.cols) ? __fsub_rn(x[j * NV + e], mean) : 0.0f;
-                x[j * NV + e] = d;  // keep the centred value; the output needs only x - mean
+                const float d = (c0 + e < a.cols) ? __fsub_rn(f[e], mean) : 0.0f;
                 q = __fadd_rn(q, __fmul_rn(d, d));
             }
         }
@@ -121,11 +155,15 @@ __global__ void __launch_bounds__(512) row_kernel(RowArgs a) {
     } else {
         float q = 0.0f;
 #pragma unroll
-        for (int i = 0; i < V * NV; ++i) q = __fadd_rn(q, __fmul_rn(x[i], x[i]));
+        for (int j = 0; j < V; ++j) {
+            float f[NV];
+            get(j, f);
+#pragma unroll
+            for (int e = 0; e < NV; ++e) q = __fadd_rn(q, __fmul_rn(f[e], f[e]));
+        }
         const float ms = __fdiv_rn(group_reduce<false>(q, tpr, red0), (float)a.cols);
         s0 = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(ms, a.eps)));
     }
-    (void)s1;
     if (!live) return;
 
     const T *wr = reinterpret_cast<const T *>(a.w);
@@ -134,7 +172,8 @@ __global__ void __launch_bounds__(512) row_kernel(RowArgs a) {
     for (int j = 0; j < V; ++j) {
         const int64_t c0 = ((int64_t)j * tpr + t) * NV;
         if (c0 >= a.cols) continue;
-        float wv[NV], bv[NV];
+        float f[NV], wv[NV], bv[NV];
+        get(j, f);
         if (OP != OP_SOFTMAX) {
             if (VEC) {
                 Pack<T>::unpack(__ldg(reinterpret_cast<const uint4 *>(wr + c0)), wv);
@@ -151,10 +190,9 @@ __global__ void __launch_bounds__(512) row_kernel(RowArgs a) {
         float o[NV];
 #pragma unroll
         for (int e = 0; e < NV; ++e) {
-            const float v = x[j * NV + e];
-            if (OP == OP_SOFTMAX) o[e] = __fdiv_rn(v, s0);
-            else if (OP == OP_LAYERNORM) o[e] = __fadd_rn(__fmul_rn(__fmul_rn(v, s0), wv[e]), bv[e]);
-            else o[e] = __fmul_rn(__fmul_rn(v, s0), wv[e]);
+            if (OP == OP_SOFTMAX) o[e] = __fdiv_rn(expf(__fsub_rn(f[e], s0)), s1);
+            else if (OP == OP_LAYERNORM) o[e] = __fadd_rn(__fmul_rn(__fmul_rn(__fsub_rn(f[e], s1), s0), wv[e]), bv[e]);
+            else o[e] = __fmul_rn(__fmul_rn(f[e], s0), wv[e]);
         }
         if (VEC) {
             st_stream(yr + c0, Pack<T>::pack(o));
@@ -227,8 +265,10 @@ __global__ void __launch_bounds__(1024) row_kernel_wide(RowArgs a) {
     }
 }
 
-// variant v: threads-per-row = base << (v / 3), CTA threads = {128, 256, 512}[v % 3]
-constexpr int ROW_VARIANTS = 9;
+// variant v: threads-per-row = base << (v / 3) for v / 3 in 0..3, CTA threads = {128, 256, 512}[v % 3];
+// base = fewest threads whose registers hold the row (min 32)
+constexpr int ROW_VARIANTS = 12;
+constexpr int kAutoVariant = 6;  // threads-per-row = base * 4, 128-thread CTAs
 
 template <typename T, int OP, bool VEC>
 int launch_v(const RowArgs &a, int v, int cta, cudaStream_t st) {
@@ -237,9 +277,10 @@ int launch_v(const RowArgs &a, int v, int cta, cudaStream_t st) {
         case 1: row_kernel<T, 1, VEC, OP><<<grid, cta, 0, st>>>(a); break;
         case 2: row_kernel<T, 2, VEC, OP><<<grid, cta, 0, st>>>(a); break;
         case 4: row_kernel<T, 4, VEC, OP><<<grid, cta, 0, st>>>(a); break;
-        case 8:
-            if constexpr (sizeof(T) == 4) {
-                row_kernel<T, 8, VEC, OP><<<grid, cta, 0, st>>>(a);
+        case 8: row_kernel<T, 8, VEC, OP><<<grid, cta, 0, st>>>(a); break;
+        case 16:
+            if constexpr (sizeof(T) == 2) {
+                row_kernel<T, 16, VEC, OP><<<grid, cta, 0, st>>>(a);
                 break;
             }
             [[fallthrough]];
@@ -251,12 +292,15 @@ int launch_v(const RowArgs &a, int v, int cta, cudaStream_t st) {
 template <typename T, int OP>
 int launch_rows(RowArgs a, int variant, cudaStream_t st, const char *name) {
     constexpr int NV = Pack<T>::N;
-    constexpr int MAXV = 32 / NV;  // at most 32 float registers of row data per thread
+    // At most 8 raw vectors (32 registers) of float32 row data per thread, 16 (64 registers) of packed
+    // float16/bfloat16: the widest row one warp holds is 1024 float32 or 4096 half values.
+    constexpr int MAXV = sizeof(T) == 4 ? 8 : 16;
     if (a.rows == 0 || a.cols == 0) return ENC_OK;
     if (a.rows > 0x7fffffffLL) return fail(ENC_ERR_UNSUPPORTED, "%s: more than 2^31-1 rows", name);
     if (variant >= ROW_VARIANTS) return fail(ENC_ERR_BAD_ARG, "%s: variant %d out of range", name, variant);
-    const int shift = variant < 0 ? 0 : variant / 3;
-    int cta = variant < 0 ? 128 : (128 << (variant % 3));
+    if (variant < 0) variant = kAutoVariant;
+    const int shift = variant / 3;
+    int cta = 128 << (variant % 3);
     int64_t tpr64 = next_pow2(cdiv(a.cols, (int64_t)NV * MAXV));
     if (tpr64 < 32) tpr64 = 32;
     tpr64 <<= shift;
@@ -294,7 +338,7 @@ template <int OP> int dispatch(const RowArgs &a, int dtype, int variant, void *s
 
 int row_variants() { return ROW_VARIANTS; }
 void row_variant_info(int v, char *out, size_t n) {
-    snprintf(out, n, "threads_per_row=base*%d cta_threads=%d (base = row length / 32 values per thread, min 32)",
+    snprintf(out, n, "threads_per_row=base*%d cta_threads=%d (base = fewest threads whose registers hold the row, min 32)",
              1 << (v / 3), 128 << (v % 3));
 }
 

@@ -72,7 +72,7 @@ unsigned int *device_error_word() {
     if (dev < 0 || dev >= MAX_DEVICES) return nullptr;
     std::lock_guard<std::mutex> lock(g_mu);
     if (!g_error_word[dev]) {
-        unsigned int *p = nullptr;
+        unsigned int *p = nullptr;  // first use on this device; must not happen inside a stream capture
         if (cudaMalloc(&p, 256) != cudaSuccess) {
             cudaGetLastError();
             return nullptr;

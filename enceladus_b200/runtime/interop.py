@@ -39,14 +39,32 @@ _pending: list[tuple[Any, np.ndarray]] = []  # (device tensor, host array) await
 _pending_lock = threading.Lock()
 
 
-def _torch():
-    import torch
+_torch_mod = None
+_TORCH_NP: dict[Any, np.dtype] = {}   # torch dtype -> NumPy dtype
+_TORCH_CODE: dict[Any, int] = {}      # torch dtype -> enc_dtype
 
-    return torch
+
+def _torch():
+    """torch, imported on first use (importing it costs seconds), with the dtype tables filled."""
+    global _torch_mod
+    if _torch_mod is None:
+        import torch
+
+        _TORCH_NP.update({torch.float32: np.dtype(np.float32), torch.float16: np.dtype(np.float16),
+                          torch.bfloat16: BF16, torch.int32: np.dtype(np.int32), torch.int8: np.dtype(np.int8),
+                          torch.int16: np.dtype(np.int16), torch.int64: np.dtype(np.int64),
+                          torch.uint8: np.dtype(np.uint8), torch.bool: np.dtype(np.bool_)})
+        _TORCH_CODE.update({t: _NP_CODES[d] for t, d in _TORCH_NP.items() if d in _NP_CODES})
+        _torch_mod = torch
+    return _torch_mod
+
+
+def tensor_type():
+    return _torch().Tensor
 
 
 def is_torch(obj: Any) -> bool:
-    return type(obj).__module__.split(".")[0] == "torch" and hasattr(obj, "data_ptr")
+    return isinstance(obj, _torch().Tensor)
 
 
 def is_array(obj: Any) -> bool:
@@ -54,13 +72,9 @@ def is_array(obj: Any) -> bool:
 
 
 def _torch_np_dtype(t: Any) -> np.dtype:
-    torch = _torch()
-    table = {torch.float32: np.dtype(np.float32), torch.float16: np.dtype(np.float16),
-             torch.bfloat16: BF16, torch.int32: np.dtype(np.int32), torch.int8: np.dtype(np.int8),
-             torch.int16: np.dtype(np.int16), torch.int64: np.dtype(np.int64),
-             torch.uint8: np.dtype(np.uint8), torch.bool: np.dtype(np.bool_)}
+    _torch()
     try:
-        return table[t.dtype]
+        return _TORCH_NP[t.dtype]
     except KeyError:
         raise TypeError(f"torch dtype {t.dtype} isn't supported by enceladus_b200") from None
 
@@ -99,6 +113,10 @@ def element_dtype(obj: Any) -> np.dtype:
 
 
 def dtype_code(obj: Any) -> int:
+    if not isinstance(obj, np.ndarray):
+        code = _TORCH_CODE.get(getattr(obj, "dtype", None))
+        if code is not None:
+            return code
     dt = element_dtype(obj)
     try:
         return _NP_CODES[dt]
@@ -109,12 +127,32 @@ def dtype_code(obj: Any) -> int:
 def _new_array(like: Any, shape: Any, dtype: Any, zero: bool) -> Any:
     shape = tuple(like.shape) if shape is None else tuple(shape)
     if isinstance(like, np.ndarray):
-        return (np.zeros if zero else np.empty)(shape, like.dtype if dtype is None else dtype)
+        dt = np.dtype(like.dtype if dtype is None else dtype)
+        big = int(np.prod(shape)) * dt.itemsize >= PINNED_MIN_BYTES
+        if big and not zero and (dt in _NP_CODES) and _torch().cuda.is_available():
+            return _pinned_empty(shape, dt)
+        return (np.zeros if zero else np.empty)(shape, dt)
     if is_torch(like):
         torch = _torch()
         td = like.dtype if dtype is None else (dtype if isinstance(dtype, torch.dtype) else _np_to_torch_dtype(dtype))
         return (torch.zeros if zero else torch.empty)(shape, dtype=td, device=like.device)
     raise TypeError(_UNSUPPORTED.format(type(like).__name__))
+
+
+PINNED_MIN_BYTES = 1 << 20
+
+
+def _pinned_empty(shape: tuple[int, ...], dt: np.dtype) -> np.ndarray:
+    """An uninitialised NumPy array in page-locked host memory.
+
+    Large NumPy outputs are copied back from the device; page-locked memory makes that copy run at
+    full PCIe speed and avoids first-touch page faults.  The block comes from torch's caching host
+    allocator, so repeated launches of one shape reuse it; the array keeps the block alive.
+    """
+    torch = _torch()
+    if BF16 is not None and dt == BF16:
+        return torch.empty(shape, dtype=torch.uint16, pin_memory=True).numpy().view(BF16)
+    return torch.empty(shape, dtype=_np_to_torch_dtype(dt), pin_memory=True).numpy()
 
 
 def new_empty(like: Any, shape: Any = None, dtype: Any = None) -> Any:

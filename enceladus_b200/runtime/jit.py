@@ -106,6 +106,7 @@ class JITFunction:
             params.append(KernelParam(n, i, tl.is_constexpr_annotation(p.annotation), p.default, n in dns))
         self.params: list[KernelParam] = params
         self.arg_names = names
+        self._constexpr_names = [p.name for p in params if p.is_constexpr]
         self._adapter = None
         self.variant: int | None = None  # forced tile variant (None = the library's choice)
         self.last_launch: dict[str, Any] = {}
@@ -158,12 +159,19 @@ class JITFunction:
             raise ValueError(f"num_warps must be a power of two from 1 to 32, but got {num_warps}")
         if dot_backend not in ("auto", "simdgroup", "mpp"):
             raise ValueError(f"dot_backend must be 'auto', 'simdgroup', or 'mpp', not {dot_backend!r}")
-        bound = self.bind(args, kwargs)
-        for p in self.params:
-            if p.is_constexpr:
-                bound[p.name] = tl.unwrap(bound[p.name])
-            elif bound[p.name] is inspect.Parameter.empty:
-                raise TypeError(f"{self.__name__}: missing argument `{p.name}`")
+        names = self.arg_names
+        if len(args) + len(kwargs) == len(names) and len(args) <= len(names):
+            # fast path: every parameter given once (positional prefix + keywords), no defaults needed
+            bound = dict(zip(names, args))
+            bound.update(kwargs)
+            if len(bound) != len(names) or any(n not in bound for n in names[len(args):]):
+                bound = self.bind(args, kwargs)
+        else:
+            bound = self.bind(args, kwargs)
+        for n in self._constexpr_names:
+            v = bound[n]
+            if isinstance(v, tl.constexpr):
+                bound[n] = v.value
         g = resolve_grid(grid, bound)
         if g[0] == 0 or g[1] == 0 or g[2] == 0:
             return  # src/enceladus/runtime/launcher.py:459-460
@@ -174,39 +182,44 @@ class JITFunction:
 
 def launch(ad, bound: dict[str, Any], grid: tuple[int, int, int], variant: int, jf: JITFunction | None) -> None:
     """Resolves array arguments to device memory, calls the adapter, writes NumPy outputs back."""
-    staged = interop.Staged()
-    resolved = dict(bound)
-    any_numpy = False
-    extents = ad.extents(bound, grid) if ad.extents is not None else {}
-    for name, v in bound.items():
-        if isinstance(v, np.ndarray):
-            any_numpy = True
-            dense = v.flags.c_contiguous and extents.get(name) == v.size
-            resolved[name] = staged.to_device(name, v, name in ad.outputs, overwritten=dense)
-        elif interop.is_torch(v):
-            if v.device.type != "cuda":
+    tensor = interop.tensor_type()
+    dev = None
+    host_names = None
+    for name in ad.array_list:
+        v = bound[name]
+        if isinstance(v, tensor):
+            if not v.is_cuda:
                 raise TypeError(f"argument `{name}` is a torch tensor on {v.device}; pass a CUDA tensor "
                                 "or a NumPy array")
-        elif name in ad.arrays:
+            if dev is None:
+                dev = v.device
+        elif isinstance(v, np.ndarray):
+            host_names = [name] if host_names is None else [*host_names, name]
+        else:
             raise TypeError(f"argument `{name}` must be a NumPy array or a torch CUDA tensor, not "
                             f"{type(v).__name__}")
     torch = interop._torch()
-    dev = next((resolved[n].device for n in ad.arrays if interop.is_torch(resolved.get(n))), None)
-    ctx = torch.cuda.device(dev) if dev is not None else _null()
-    with ctx:
-        ad.launch(resolved, grid, variant, interop.current_stream())
-        if any_numpy:
-            staged.finish()
+    if host_names is None:  # hot path: every array already lives on the device
+        if dev.index != torch.cuda.current_device():
+            with torch.cuda.device(dev):
+                ad.fn(bound, grid, variant, interop.current_stream())
+        else:
+            ad.fn(bound, grid, variant, interop.current_stream())
+        return
+    staged = interop.Staged()
+    resolved = dict(bound)
+    extents = ad.extents(bound, grid) if ad.extents is not None else {}
+    for name in host_names:
+        v = bound[name]
+        dense = v.flags.c_contiguous and extents.get(name) == v.size
+        resolved[name] = staged.to_device(name, v, name in ad.outputs, overwritten=dense)
+    if dev is not None and dev.index != torch.cuda.current_device():
+        raise ValueError("NumPy arguments are staged on the current CUDA device, but the tensor arguments "
+                         f"live on {dev}; make it current with torch.cuda.set_device first")
+    ad.fn(resolved, grid, variant, interop.current_stream())
+    staged.finish()
     if jf is not None:
         jf.last_launch = {"h2d_bytes": staged.h2d_bytes, "d2h_bytes": staged.d2h_bytes, "variant": variant}
-
-
-class _null:
-    def __enter__(self):
-        return self
-
-    def __exit__(self, *a):
-        return False
 
 
 def jit(fn: Callable[..., Any] | None = None, *, interpret: bool | None = None,

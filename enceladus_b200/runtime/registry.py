@@ -30,6 +30,9 @@ class Adapter:
     # output of exactly that size is fully overwritten, so its old contents need not be copied in
     extents: Callable[[dict[str, Any], tuple[int, int, int]], dict[str, int]] | None = field(repr=False, default=None)
 
+    def __post_init__(self) -> None:
+        self.array_list = tuple(p for p in self.params if p in self.arrays)
+
     def launch(self, a: dict[str, Any], grid: tuple[int, int, int], variant: int, stream: int) -> None:
         self.fn(a, grid, variant, stream)
 
