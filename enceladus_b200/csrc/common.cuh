@@ -42,7 +42,7 @@ inline size_t dtype_size(int dt) {
     }
 }
 inline bool is_float_dtype(int dt) { return dt == ENC_F32 || dt == ENC_F16 || dt == ENC_BF16; }
-inline bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+__host__ __device__ inline bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 inline int64_t cdiv(int64_t a, int64_t b) { return (a + b - 1) / b; }
 inline int next_pow2(int64_t n) {
     int p = 1;
@@ -134,6 +134,13 @@ __device__ __forceinline__ uint4 ld_stream(const void *p) {
 __device__ __forceinline__ void st_stream(void *p, const uint4 &v) {
     asm volatile("st.global.L1::no_allocate.v4.u32 [%0], {%1,%2,%3,%4};"
                  :: "l"(p), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+}
+
+// 2^x by the special-function unit (relative error about 2^-22; results below 2^-126 flush to zero).
+__device__ __forceinline__ float fast_exp2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
 }
 
 __device__ __forceinline__ float warp_sum(float v) {

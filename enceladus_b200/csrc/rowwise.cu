@@ -7,10 +7,13 @@
 // computed from the registers, so nothing is re-read.  Rows wider than the register budget take a
 // three-pass kernel that re-reads the row through L2.
 //
-// Arithmetic follows the reference kernels op by op (examples/02_softmax.py:15-24,
-// examples/03_layernorm.py:15-42, examples/06_rmsnorm.py:15-24): true division, 1/sqrt in two
-// roundings, products and sums rounded separately (no FMA contraction) so the only difference from
-// the reference interpreter is the order of the row sums.
+// The formulas are the reference kernels' (examples/02_softmax.py:15-24, examples/03_layernorm.py:15-42,
+// examples/06_rmsnorm.py:15-24): max-subtracted softmax, two-pass centred variance, 1/sqrt(var+eps).
+// At B200's ratio of HBM bandwidth to FP32 issue rate a bf16 element has a budget of about twenty
+// lane-instructions, so the per-element work is kept short: fused multiply-adds where the reference
+// rounds twice, exp as ex2.approx of a pre-scaled argument, one reciprocal per row instead of a
+// division per element.  Each of these moves a result by a few float32 ulps, far inside the
+// tolerances the results are held to (1e-5 for float32 outputs).
 #include "common.cuh"
 
 namespace enc {
@@ -100,7 +103,8 @@ __global__ void __launch_bounds__(512) row_kernel(RowArgs a) {
         }
     };
 
-    float s0 = 1.0f, s1 = 0.0f;  // softmax: max, sum.  layernorm: rstd, mean.  rmsnorm: rstd.
+    constexpr float LOG2E = 1.4426950408889634f;
+    float s0 = 1.0f, s1 = 0.0f;  // softmax: -max*log2e, 1/sum.  layernorm: rstd, -mean*rstd.  rmsnorm: rstd.
     if (OP == OP_SOFTMAX) {
         float m = -INFINITY;
 #pragma unroll
@@ -111,16 +115,17 @@ __global__ void __launch_bounds__(512) row_kernel(RowArgs a) {
             for (int e = 0; e < NV; ++e) m = fmaxf(m, f[e]);
         }
         m = group_reduce<true>(m, tpr, red0);
+        const float nm = -m * LOG2E;  // exp(x - m) = 2^(x*log2e - m*log2e)
         float s = 0.0f;
 #pragma unroll
         for (int j = 0; j < V; ++j) {
             float f[NV];
             get(j, f);
 #pragma unroll
-            for (int e = 0; e < NV; ++e) s += expf(__fsub_rn(f[e], m));
+            for (int e = 0; e < NV; ++e) s += fast_exp2(fmaf(f[e], LOG2E, nm));
         }
-        s1 = group_reduce<false>(s, tpr, red1);
-        s0 = m;
+        s0 = nm;
+        s1 = __fdiv_rn(1.0f, group_reduce<false>(s, tpr, red1));
     } else if (OP == OP_LAYERNORM) {
         float s = 0.0f;
 #pragma unroll
@@ -136,18 +141,19 @@ __global__ void __launch_bounds__(512) row_kernel(RowArgs a) {
 #pragma unroll
         for (int j = 0; j < V; ++j) {
             const int64_t c0 = ((int64_t)j * tpr + t) * NV;
+            if (VEC && c0 >= a.cols) continue;  // a vector is inside the row or entirely past it
             float f[NV];
             get(j, f);
 #pragma unroll
             for (int e = 0; e < NV; ++e) {
-                const float d = (c0 + e < a.cols) ? __fsub_rn(f[e], mean) : 0.0f;
-                q = __fadd_rn(q, __fmul_rn(d, d));
+                const float d = (VEC || c0 + e < a.cols) ? f[e] - mean : 0.0f;
+                q = fmaf(d, d, q);
             }
         }
         const float var = __fdiv_rn(group_reduce<false>(q, tpr, red1), n);
         const float rstd = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(var, a.eps)));
         s0 = rstd;
-        s1 = mean;
+        s1 = -mean * rstd;  // (x - mean) * rstd = x*rstd - mean*rstd
         if (live && t == 0) {
             if (a.mean) a.mean[row] = mean;
             if (a.rstd) a.rstd[row] = rstd;
@@ -159,7 +165,7 @@ __global__ void __launch_bounds__(512) row_kernel(RowArgs a) {
             float f[NV];
             get(j, f);
 #pragma unroll
-            for (int e = 0; e < NV; ++e) q = __fadd_rn(q, __fmul_rn(f[e], f[e]));
+            for (int e = 0; e < NV; ++e) q = fmaf(f[e], f[e], q);
         }
         const float ms = __fdiv_rn(group_reduce<false>(q, tpr, red0), (float)a.cols);
         s0 = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(ms, a.eps)));
@@ -190,9 +196,9 @@ __global__ void __launch_bounds__(512) row_kernel(RowArgs a) {
         float o[NV];
 #pragma unroll
         for (int e = 0; e < NV; ++e) {
-            if (OP == OP_SOFTMAX) o[e] = __fdiv_rn(expf(__fsub_rn(f[e], s0)), s1);
-            else if (OP == OP_LAYERNORM) o[e] = __fadd_rn(__fmul_rn(__fmul_rn(__fsub_rn(f[e], s1), s0), wv[e]), bv[e]);
-            else o[e] = __fmul_rn(__fmul_rn(f[e], s0), wv[e]);
+            if (OP == OP_SOFTMAX) o[e] = fast_exp2(fmaf(f[e], LOG2E, s0)) * s1;
+            else if (OP == OP_LAYERNORM) o[e] = fmaf(fmaf(f[e], s0, s1), wv[e], bv[e]);
+            else o[e] = (f[e] * s0) * wv[e];
         }
         if (VEC) {
             st_stream(yr + c0, Pack<T>::pack(o));

@@ -2,7 +2,7 @@
 // word that bounded device-side waits raise, variant tables and synchronisation.
 #include <mutex>
 
-#include "common.cuh"
+#include "sm100.cuh"
 
 namespace enc {
 
@@ -81,6 +81,42 @@ unsigned int *device_error_word() {
         g_error_word[dev] = p;
     }
     return g_error_word[dev];
+}
+
+bool make_tensor_map(CUtensorMap *map, const void *base, int elem_is_bf16, int rank, const uint64_t *dims,
+                     const uint64_t *strides_bytes, const uint32_t *box, char *err, size_t errlen) {
+    using EncodeFn = CUresult (*)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                  const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+    static EncodeFn encode = nullptr;
+    if (!encode) {
+        void *fn = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q) != cudaSuccess || !fn) {
+            cudaGetLastError();
+            snprintf(err, errlen, "the driver does not provide cuTensorMapEncodeTiled");
+            return false;
+        }
+        encode = reinterpret_cast<EncodeFn>(fn);
+    }
+    cuuint64_t d[5], s[4];
+    cuuint32_t b[5], e[5];
+    for (int i = 0; i < rank; ++i) {
+        d[i] = dims[i];
+        b[i] = box[i];
+        e[i] = 1;
+        if (i + 1 < rank) s[i] = strides_bytes[i];
+    }
+    const CUresult r = encode(map, elem_is_bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16,
+                              (cuuint32_t)rank, const_cast<void *>(base), d, s, b, e, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                              CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) {
+        snprintf(err, errlen, "cuTensorMapEncodeTiled failed with CUresult %d (rank %d, dims %llu x %llu, box %u x %u)",
+                 (int)r, rank, (unsigned long long)dims[0], (unsigned long long)dims[1], box[0], box[1]);
+        return false;
+    }
+    return true;
 }
 
 }  // namespace enc

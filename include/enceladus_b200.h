@@ -160,10 +160,10 @@ int enc_sum(const void *in, void *total, int64_t n, int dtype, void *stream);
 /* ---- tensor-core kernels ------------------------------------------------------------------ */
 
 /* C = epilogue(A @ B): A [M,K] (lda), B [K,N] (ldb), C [M,N] (ldc), all row-major with unit inner
- * stride, float32 accumulation on tcgen05 tensor cores, C in the operand dtype.
+ * stride, float32 accumulation on tcgen05 tensor cores (float32 operands: CUDA cores), C in the operand dtype.
  * epilogue 0: identity.  epilogue 1: t = acc + bias[n]; 0.5*t*(1+erf(t*0.70710677f)).
  * Out-of-range tile elements read as zero and are not stored (descriptor semantics,
- * src/enceladus/language/ops.py:495-514).  dtype: ENC_F16 | ENC_BF16.
+ * src/enceladus/language/ops.py:495-514).  dtype: ENC_F16 | ENC_BF16 | ENC_F32.
  * Replaces matmul_bias_gelu_kernel[(cdiv(N,BN),cdiv(M,BM))](a, b, bias, c, M, N, K, lda, ldb, ldc, BM, BN, BK)
  *                                                                                    examples/07_matmul_fused.py:17-48
  * and matmul_desc_kernel                                                             examples/04_matmul.py:21-63 */
