@@ -1,9 +1,471 @@
-#include "common.cuh"
+// Flash-attention forward on the tcgen05 tensor cores of sm_100a.
+//
+// One CTA per (batch*head, 128 query rows).  Keys and values stream through a TMA-fed ring of
+// 128-byte-swizzled shared memory in blocks of 128 rows; both matrix products run as tcgen05.mma with
+// float32 accumulators in tensor memory:
+//     S = Q K^T    (128 x 128, A = Q K-major, B = K block K-major)      -> TMEM, double buffered
+//     O += P V     (128 x D,   A = P K-major in shared memory, B = V block MN-major) -> TMEM
+//   warp 0      TMA producer (Q once, then K0 V0 K1 V1 ... through the ring)
+//   warp 1      MMA issuer; S of block j+1 is issued before P V of block j so that the tensor core
+//               works while the softmax warps are busy with block j
+//   warps 2..5  softmax: thread i owns query row i.  Base-2 online softmax in float32 on the scaled
+//               scores (scale * log2 e folded into one multiply), masked with -inf outside the sequence
+//               and above the diagonal; P is rounded to the input type and written to shared memory in
+//               the swizzled layout the MMA reads; the running output is rescaled in TMEM only when
+//               the row maximum has grown by more than 2^8 since the last rescale (the statistics stay
+//               exact: l and the final 1/l use the same reference maximum).  Finally O / l is stored,
+//               and lse = ln2 * (m + log2 l) when requested.
+// The arithmetic follows the reference kernel (examples/08_flash_attention.py:30-70): scores scaled
+// after the float32 dot, exp2 of (score - max), P cast to the input dtype before the second dot, a true
+// division by l at the end.  Causal launches skip key blocks above the diagonal.
+//
+// Shapes this kernel does not take (head_dim other than 64/128, float32 inputs, strides that TMA
+// cannot describe) run on a CUDA-core kernel with the same arithmetic.
+#include "sm100.cuh"
+
 namespace enc {
-int attention_variants() { return 0; }
-void attention_variant_info(int, char *out, size_t n) { snprintf(out, n, "-"); }
+namespace {
+
+using namespace sm100;
+
+constexpr int BM = 128, BN = 128;
+constexpr int kThreads = 192;
+constexpr float LOG2E = 1.4426950408889634f, LN2 = 0.6931471805599453f;
+constexpr float RESCALE_THRESHOLD = 8.0f;  // in log2 units
+
+struct AttnArgs {
+    void *o;
+    float *lse;
+    int64_t seq, stride_h, stride_m;
+    float qk_scale;  // sm_scale * log2(e), rounded to float32 once
+    int causal;
+    int is_bf16;
+    unsigned *error;
+};
+
+template <int D, int STAGES> struct AttnSmem {
+    static constexpr int TILE = BM * D * 2;          // one 128-row block of Q, K or V
+    static constexpr int Q_OFF = 0;
+    static constexpr int KV_OFF = TILE;
+    static constexpr int P_OFF = KV_OFF + STAGES * TILE;
+    static constexpr int P_BYTES = BM * BN * 2;
+    static constexpr int BAR_OFF = P_OFF + P_BYTES;
+    static constexpr int NBARS = 1 + 2 * STAGES + 2 + 2 + 1 + 1 + 1;  // q, kv full/empty, s full/empty, p full/empty, o
+    static constexpr int TOTAL = BAR_OFF + NBARS * 8 + 16;
+};
+
+template <typename T, int D, int STAGES>
+__global__ void __launch_bounds__(kThreads, 1)
+attention_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
+                    const __grid_constant__ CUtensorMap tm_v, AttnArgs a) {
+    using L = AttnSmem<D, STAGES>;
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
+    uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint64_t *q_full = reinterpret_cast<uint64_t *>(smem + L::BAR_OFF);
+    uint64_t *kv_full = q_full + 1;
+    uint64_t *kv_empty = kv_full + STAGES;
+    uint64_t *s_full = kv_empty + STAGES;  // [2]
+    uint64_t *s_empty = s_full + 2;        // [2]
+    uint64_t *p_full = s_empty + 2;
+    uint64_t *p_empty = p_full + 1;
+    uint64_t *o_full = p_empty + 1;
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(o_full + 1);
+    volatile uint32_t *abort = tmem_slot + 1;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    // heavy (late) query blocks first when causal, so the tail of the grid is made of short CTAs
+    const int qb = a.causal ? (int)(gridDim.x - 1 - blockIdx.x) : (int)blockIdx.x;
+    const int bh = blockIdx.y;
+    const int64_t m0 = (int64_t)qb * BM;
+    const int64_t kv_hi = a.causal ? (m0 + BM < a.seq ? m0 + BM : a.seq) : a.seq;
+    const int nkv = (int)((kv_hi + BN - 1) / BN);
+    constexpr uint32_t TMEM_COLS = 512;
+    constexpr uint32_t S_COL = 0, O_COL = 256;
+
+    if (threadIdx.x == 0) {
+        mbar_init(q_full, 1);
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(&kv_full[s], 1);
+            mbar_init(&kv_empty[s], 1);
+        }
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(&s_full[i], 1);
+            mbar_init(&s_empty[i], 128);
+        }
+        mbar_init(p_full, 128);
+        mbar_init(p_empty, 1);
+        mbar_init(o_full, 1);
+        *abort = 0;
+        fence_barrier_init();
+        prefetch_tensormap(&tm_q);
+        prefetch_tensormap(&tm_k);
+        prefetch_tensormap(&tm_v);
+    }
+    if (warp == 1) tmem_alloc(tmem_slot, TMEM_COLS);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        // ---------------- TMA producer ----------------
+        if (lane == 0) {
+            mbar_expect_tx(q_full, L::TILE);
+#pragma unroll
+            for (int b = 0; b < D / 64; ++b) tma_load_3d(smem + L::Q_OFF + b * (BM * 128), &tm_q, q_full, b * 64, (int)m0, bh);
+            bool ok = true;
+            uint32_t stage = 0, phase = 0;
+            for (int it = 0; it < 2 * nkv && ok; ++it) {  // K0 V0 K1 V1 ...
+                const int j = it >> 1;
+                ok = mbar_wait(&kv_empty[stage], phase ^ 1, abort);
+                if (!ok) break;
+                uint8_t *dst = smem + L::KV_OFF + stage * L::TILE;
+                mbar_expect_tx(&kv_full[stage], L::TILE);
+                const CUtensorMap *tm = (it & 1) ? &tm_v : &tm_k;
+#pragma unroll
+                for (int b = 0; b < D / 64; ++b) tma_load_3d(dst + b * (BN * 128), tm, &kv_full[stage], b * 64, j * BN, bh);
+                if (++stage == STAGES) { stage = 0; phase ^= 1; }
+            }
+            if (*abort) {  // drain our own copies before the CTA exits
+                for (uint32_t i = 0; i < (1u << 16) && !mbar_try_wait(q_full, 0); ++i) {}
+                for (uint32_t s = 0; s < (uint32_t)STAGES; ++s) {
+                    const uint32_t p = s < stage ? phase : phase ^ 1;
+                    for (uint32_t i = 0; i < (1u << 16) && !mbar_try_wait(&kv_full[s], p); ++i) {}
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------- MMA issuer ----------------
+        if (lane == 0) {
+            const uint32_t idesc_s = idesc_f16(a.is_bf16, /*b_mn_major=*/false, BM, BN);
+            const uint32_t idesc_o = idesc_f16(a.is_bf16, /*b_mn_major=*/true, BM, D);
+            const uint32_t sq = smem_u32(smem + L::Q_OFF), sp = smem_u32(smem + L::P_OFF);
+            bool ok = mbar_wait(q_full, 0, abort);
+            // ring position of tile `it` (K_j = 2j, V_j = 2j+1)
+            auto slot = [&](int it, uint32_t &stage, uint32_t &phase) { stage = it % STAGES; phase = (it / STAGES) & 1; };
+            auto issue_s = [&](int j) -> bool {  // S_j = Q K_j^T into S buffer j & 1
+                uint32_t stage, phase;
+                slot(2 * j, stage, phase);
+                if (!mbar_wait(&kv_full[stage], phase, abort)) return false;
+                if (!mbar_wait(&s_empty[j & 1], ((j >> 1) & 1) ^ 1, abort)) return false;
+                tc_fence_after();
+                const uint32_t sk = smem_u32(smem + L::KV_OFF + stage * L::TILE);
+                const uint32_t d_tmem = tmem_base + S_COL + (j & 1) * BN;
+#pragma unroll
+                for (int kk = 0; kk < D / 16; ++kk) {
+                    const uint32_t off = (kk >> 2) * (BM * 128) + (kk & 3) * 32;  // 64-wide box, then 32 bytes per step
+                    tc_mma_f16(d_tmem, smem_desc_sw128(sq + off, 16, 1024), smem_desc_sw128(sk + off, 16, 1024), idesc_s, kk != 0);
+                }
+                tc_commit(&kv_empty[stage]);
+                tc_commit(&s_full[j & 1]);
+                return true;
+            };
+            if (ok && nkv > 0) ok = issue_s(0);
+            for (int j = 0; j < nkv && ok; ++j) {
+                if (j + 1 < nkv) {
+                    ok = issue_s(j + 1);
+                    if (!ok) break;
+                }
+                uint32_t stage, phase;
+                slot(2 * j + 1, stage, phase);
+                ok = mbar_wait(&kv_full[stage], phase, abort) && mbar_wait(p_full, j & 1, abort);
+                if (!ok) break;
+                tc_fence_after();
+                const uint32_t sv = smem_u32(smem + L::KV_OFF + stage * L::TILE);
+#pragma unroll
+                for (int kk = 0; kk < BN / 16; ++kk) {
+                    const uint32_t poff = (kk >> 2) * (BM * 128) + (kk & 3) * 32;
+                    // V block: 64-wide column boxes BN*128 bytes apart, 16 key rows = 2048 bytes per step
+                    tc_mma_f16(tmem_base + O_COL, smem_desc_sw128(sp + poff, 16, 1024),
+                               smem_desc_sw128(sv + kk * 2048, BN * 128, 1024), idesc_o, (j | kk) != 0);
+                }
+                tc_commit(&kv_empty[stage]);
+                tc_commit(p_empty);
+            }
+            if (ok) tc_commit(o_full);
+        }
+    } else {
+        // ---------------- softmax / epilogue warps ----------------
+        const int quarter = warp & 3;
+        const int r = quarter * 32 + lane;  // query row inside the tile == TMEM lane
+        const int64_t row = m0 + r;
+        const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
+        uint8_t *p_row = smem + L::P_OFF + r * 128;
+        float m_ref = -INFINITY, l = 0.0f;
+        bool ok = true;
+        for (int j = 0; j < nkv && ok; ++j) {
+            ok = mbar_wait(&s_full[j & 1], (j >> 1) & 1, abort);
+            if (!ok) break;
+            tc_fence_after();
+            const uint32_t t_s = tmem_base + lane_addr + S_COL + (j & 1) * BN;
+            const int64_t n0 = (int64_t)j * BN;
+            const bool need_mask = (n0 + BN > a.seq) || (a.causal && n0 + BN > m0);
+            // pass 1: row maximum of the scaled, masked scores
+            float mx = -INFINITY;
+#pragma unroll 1
+            for (int c0 = 0; c0 < BN; c0 += 32) {
+                uint32_t v[32];
+                tmem_ld_32x32(t_s + c0, v);
+                tmem_ld_wait();
+#pragma unroll
+                for (int i = 0; i < 32; ++i) {
+                    float s = __uint_as_float(v[i]) * a.qk_scale;
+                    if (need_mask) {
+                        const int64_t col = n0 + c0 + i;
+                        if (col >= a.seq || (a.causal && col > row)) s = -INFINITY;
+                    }
+                    mx = fmaxf(mx, s);
+                }
+            }
+            const float m_new = fmaxf(m_ref, mx);
+            // rescale only when the maximum moved far enough for exp2(s - m_ref) to risk overflow
+            const bool rescale = m_new > m_ref + RESCALE_THRESHOLD;  // also true for the first finite maximum
+            float alpha = 1.0f;
+            if (rescale) {
+                alpha = m_ref == -INFINITY ? 0.0f : fast_exp2(m_ref - m_new);
+                m_ref = m_new;
+            }
+            // P(j-1) V has finished: the P buffer is free and O is quiescent
+            ok = mbar_wait(p_empty, (j & 1) ^ 1, abort);
+            if (!ok) break;
+            tc_fence_after();
+            if (j > 0 && __any_sync(0xffffffffu, rescale)) {
+#pragma unroll 1
+                for (int c0 = 0; c0 < D; c0 += 32) {
+                    uint32_t v[32];
+                    tmem_ld_32x32(tmem_base + lane_addr + O_COL + c0, v);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * alpha);
+                    tmem_st_32x32(tmem_base + lane_addr + O_COL + c0, v);
+                }
+                tmem_st_wait();
+            }
+            l *= alpha;
+            // pass 2: p = 2^(s - m_ref), row sum in float32, P rounded to the input type into shared memory
+            const float neg_m = m_ref == -INFINITY ? 0.0f : -m_ref;
+            float sum = 0.0f;
+#pragma unroll 1
+            for (int c0 = 0; c0 < BN; c0 += 32) {
+                uint32_t v[32];
+                tmem_ld_32x32(t_s + c0, v);
+                tmem_ld_wait();
+                float p[32];
+#pragma unroll
+                for (int i = 0; i < 32; ++i) {
+                    float s = fmaf(__uint_as_float(v[i]), a.qk_scale, neg_m);
+                    if (need_mask) {
+                        const int64_t col = n0 + c0 + i;
+                        if (col >= a.seq || (a.causal && col > row)) s = -INFINITY;
+                    }
+                    p[i] = fast_exp2(s);
+                    sum += p[i];
+                }
+                // 32 columns = four 16-byte chunks of this row inside the 64-wide box (c0 / 64)
+                uint8_t *box = p_row + (c0 >> 6) * (BM * 128);
+#pragma unroll
+                for (int q4 = 0; q4 < 4; ++q4) {
+                    const int chunk = ((c0 & 63) >> 3) + q4;
+                    *reinterpret_cast<uint4 *>(box + ((chunk ^ (r & 7)) << 4)) = Pack<T>::pack(p + 8 * q4);
+                }
+            }
+            l += sum;
+            tc_fence_before();
+            mbar_arrive(&s_empty[j & 1]);  // this thread is done reading S(j)
+            fence_proxy_async();           // make the P stores visible to the tensor core
+            mbar_arrive(p_full);
+        }
+        // ---- epilogue: O / l ----
+        if (ok && nkv > 0) ok = mbar_wait(o_full, 0, abort);
+        if (ok) {
+            tc_fence_after();
+            T *o = reinterpret_cast<T *>(a.o) + (int64_t)bh * a.stride_h + row * a.stride_m;
+#pragma unroll 1
+            for (int c0 = 0; c0 < D; c0 += 32) {
+                uint32_t v[32];
+                if (nkv > 0) {
+                    tmem_ld_32x32(tmem_base + lane_addr + O_COL + c0, v);
+                    tmem_ld_wait();
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) v[i] = 0;
+                }
+                if (row < a.seq) {
+                    float f[32];
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) f[i] = __fdiv_rn(__uint_as_float(v[i]), l);
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) *reinterpret_cast<uint4 *>(o + c0 + 8 * i) = Pack<T>::pack(f + 8 * i);
+                }
+            }
+            if (a.lse && row < a.seq) a.lse[(int64_t)bh * a.seq + row] = (m_ref + log2f(l)) * LN2;
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (threadIdx.x == 0 && *abort) atomicExch(a.error, 4u);
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, TMEM_COLS);
+    }
 }
-extern "C" int enc_attention_fwd(const void *, const void *, const void *, void *, float *, int64_t, int64_t, int64_t, int64_t, int64_t, float, int, int, int, void *) {
+
+// ---- CUDA-core kernel: any head_dim <= 128, any of the three dtypes, any strides -------------------
+// One CTA of 128 threads per (batch*head, 16 query rows): 8 threads share a row and split head_dim.
+template <typename T>
+__global__ void __launch_bounds__(128) attention_simple_kernel(const T *q, const T *k, const T *v, T *o, float *lse,
+                                                              int64_t seq, int d, int64_t stride_h, int64_t stride_m,
+                                                              float qk_scale, int causal) {
+    constexpr int ROWS = 16, LANES = 8, KV = 32;
+    __shared__ float sk[KV][128 + 1], sv[KV][128 + 1];
+    const int bh = blockIdx.y;
+    const int rl = threadIdx.x / LANES, part = threadIdx.x % LANES;
+    const int64_t row = (int64_t)blockIdx.x * ROWS + rl;
+    const T *qb = q + (int64_t)bh * stride_h, *kb = k + (int64_t)bh * stride_h, *vb = v + (int64_t)bh * stride_h;
+    const bool is_half = sizeof(T) == 2;
+    float qr[16], acc[16];  // this thread's slice of head_dim: elements part, part + 8, ...
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+        const int c = part + i * LANES;
+        qr[i] = (row < seq && c < d) ? to_f32(qb[row * stride_m + c]) : 0.0f;
+        acc[i] = 0.0f;
+    }
+    float m_i = -INFINITY, l_i = 0.0f;
+    const int64_t m_last = (int64_t)blockIdx.x * ROWS + ROWS - 1;
+    const int64_t hi = causal ? (m_last + 1 < seq ? m_last + 1 : seq) : seq;
+    for (int64_t n0 = 0; n0 < hi; n0 += KV) {
+        __syncthreads();
+        for (int i = threadIdx.x; i < KV * d; i += blockDim.x) {
+            const int rr = i / d, c = i % d;
+            const bool okr = n0 + rr < seq;
+            sk[rr][c] = okr ? to_f32(kb[(n0 + rr) * stride_m + c]) : 0.0f;
+            sv[rr][c] = okr ? to_f32(vb[(n0 + rr) * stride_m + c]) : 0.0f;
+        }
+        __syncthreads();
+        float s[KV];
+        float mx = -INFINITY;
+#pragma unroll 4
+        for (int jj = 0; jj < KV; ++jj) {
+            float dot = 0.0f;
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+                const int c = part + i * LANES;
+                if (c < d) dot = fmaf(qr[i], sk[jj][c], dot);
+            }
+            dot += __shfl_xor_sync(0xffffffffu, dot, 1);
+            dot += __shfl_xor_sync(0xffffffffu, dot, 2);
+            dot += __shfl_xor_sync(0xffffffffu, dot, 4);
+            const int64_t col = n0 + jj;
+            float sc = dot * qk_scale;
+            if (col >= seq || (causal && col > row)) sc = -INFINITY;
+            s[jj] = sc;
+            mx = fmaxf(mx, sc);
+        }
+        const float m_new = fmaxf(m_i, mx);
+        const float m_safe = m_new == -INFINITY ? 0.0f : m_new;
+        const float alpha = m_i == -INFINITY ? 0.0f : exp2f(m_i - m_safe);
+        float sum = 0.0f;
+#pragma unroll
+        for (int i = 0; i < 16; ++i) acc[i] *= alpha;
+#pragma unroll 4
+        for (int jj = 0; jj < KV; ++jj) {
+            const float p = exp2f(s[jj] - m_safe);
+            sum += p;
+            const float pr = is_half ? to_f32(from_f32<T>(p)) : p;  // P rounded to the input type
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+                const int c = part + i * LANES;
+                if (c < d) acc[i] = fmaf(pr, sv[jj][c], acc[i]);
+            }
+        }
+        l_i = l_i * alpha + sum;
+        m_i = m_new;
+    }
+    if (row < seq) {
+        T *ob = o + (int64_t)bh * stride_h + row * stride_m;
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+            const int c = part + i * LANES;
+            if (c < d) ob[c] = from_f32<T>(__fdiv_rn(acc[i], l_i));
+        }
+        if (lse && part == 0) lse[(int64_t)bh * seq + row] = (m_i + log2f(l_i)) * LN2;
+    }
+}
+
+constexpr int ATTN_VARIANTS = 2;  // 0: 128x128 tiles, 4-deep K/V ring; 1: 3-deep ring
+
+template <typename T, int D, int STAGES>
+int launch_tc(const void *q, const void *k, const void *v, const AttnArgs &args, int64_t bh, cudaStream_t st) {
+    using L = AttnSmem<D, STAGES>;
+    char err[256];
+    CUtensorMap tq, tk, tv;
+    const uint64_t dims[3] = {(uint64_t)D, (uint64_t)args.seq, (uint64_t)bh};
+    const uint64_t strides[2] = {(uint64_t)args.stride_m * 2, (uint64_t)args.stride_h * 2};
+    const uint32_t box[3] = {64, BM, 1};
+    if (!make_tensor_map(&tq, q, args.is_bf16, 3, dims, strides, box, err, sizeof(err)) ||
+        !make_tensor_map(&tk, k, args.is_bf16, 3, dims, strides, box, err, sizeof(err)) ||
+        !make_tensor_map(&tv, v, args.is_bf16, 3, dims, strides, box, err, sizeof(err)))
+        return fail(ENC_ERR_LAUNCH, "enc_attention_fwd: %s", err);
+    auto kern = attention_tc_kernel<T, D, STAGES>;
+    const int smem = L::TOTAL + 1024;
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) return fail(ENC_ERR_LAUNCH, "enc_attention_fwd: cannot opt in to %d bytes of shared memory: %s", smem, cudaGetErrorString(e));
+    dim3 grid((unsigned)cdiv(args.seq, BM), (unsigned)bh);
+    kern<<<grid, kThreads, smem, st>>>(tq, tk, tv, args);
+    return check_launch("enc_attention_fwd");
+}
+
+template <typename T>
+int launch_attention(const void *q, const void *k, const void *v, AttnArgs args, int64_t bh, int64_t d, int variant,
+                     cudaStream_t st) {
+    const bool tc = sizeof(T) == 2 && (d == 64 || d == 128) && aligned16(q) && aligned16(k) && aligned16(v) &&
+                    aligned16(args.o) && args.stride_m % 8 == 0 && args.stride_h % 8 == 0 && bh <= 65535 &&
+                    args.seq < (1LL << 31);
+    if (!tc) {
+        if (bh > 65535) return fail(ENC_ERR_UNSUPPORTED, "enc_attention_fwd: more than 65535 (batch, head) slices");
+        dim3 grid((unsigned)cdiv(args.seq, 16), (unsigned)bh);
+        attention_simple_kernel<T><<<grid, 128, 0, st>>>((const T *)q, (const T *)k, (const T *)v, (T *)args.o, args.lse,
+                                                         args.seq, (int)d, args.stride_h, args.stride_m, args.qk_scale,
+                                                         args.causal);
+        return check_launch("enc_attention_fwd");
+    }
+    args.error = device_error_word();
+    if (!args.error) return fail(ENC_ERR_NO_MEMORY, "enc_attention_fwd: cannot allocate the device status word");
+    if constexpr (sizeof(T) == 2) {
+        if (d == 128) {
+            return variant == 1 ? launch_tc<T, 128, 3>(q, k, v, args, bh, st) : launch_tc<T, 128, 4>(q, k, v, args, bh, st);
+        }
+        return variant == 1 ? launch_tc<T, 64, 3>(q, k, v, args, bh, st) : launch_tc<T, 64, 4>(q, k, v, args, bh, st);
+    }
+    return fail(ENC_ERR_UNSUPPORTED, "enc_attention_fwd: unreachable");
+}
+
+}  // namespace
+
+int attention_variants() { return ATTN_VARIANTS; }
+void attention_variant_info(int v, char *out, size_t n) {
+    snprintf(out, n, "block_m=128 block_n=128 kv_stages=%d tcgen05 S/O in TMEM, P through shared memory", v == 1 ? 3 : 4);
+}
+
+}  // namespace enc
+
+extern "C" int enc_attention_fwd(const void *q, const void *k, const void *v, void *o, float *lse, int64_t bh,
+                                 int64_t seq, int64_t head_dim, int64_t stride_h, int64_t stride_m, float sm_scale,
+                                 int causal, int dtype, int variant, void *stream) {
     ENC_PROLOGUE();
-    return enc::fail(ENC_ERR_UNSUPPORTED, "enc_attention_fwd: not built yet");
+    if (bh < 0 || seq < 0 || head_dim <= 0) return enc::fail(ENC_ERR_BAD_ARG, "enc_attention_fwd: bad shape");
+    if (bh == 0 || seq == 0) return ENC_OK;
+    if (!q || !k || !v || !o) return enc::fail(ENC_ERR_BAD_ARG, "enc_attention_fwd: NULL tensor");
+    if (head_dim > 128) return enc::fail(ENC_ERR_UNSUPPORTED, "enc_attention_fwd: head_dim %lld > 128", (long long)head_dim);
+    if (stride_m < head_dim) return enc::fail(ENC_ERR_BAD_ARG, "enc_attention_fwd: row stride smaller than head_dim");
+    if (variant >= enc::ATTN_VARIANTS) return enc::fail(ENC_ERR_BAD_ARG, "enc_attention_fwd: variant %d out of range", variant);
+    enc::AttnArgs args{o, lse, seq, stride_h, stride_m, sm_scale * enc::LOG2E, causal ? 1 : 0, dtype == ENC_BF16 ? 1 : 0, nullptr};
+    cudaStream_t st = enc::as_stream(stream);
+    switch (dtype) {
+        case ENC_F16: return enc::launch_attention<__half>(q, k, v, args, bh, head_dim, variant, st);
+        case ENC_BF16: return enc::launch_attention<__nv_bfloat16>(q, k, v, args, bh, head_dim, variant, st);
+        case ENC_F32: return enc::launch_attention<float>(q, k, v, args, bh, head_dim, variant, st);
+        default: return enc::fail(ENC_ERR_BAD_ARG, "enc_attention_fwd: dtype %d is not float16, bfloat16 or float32", dtype);
+    }
 }

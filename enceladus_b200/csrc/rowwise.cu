@@ -14,7 +14,11 @@
 // rounds twice, exp as ex2.approx of a pre-scaled argument, one reciprocal per row instead of a
 // division per element.  Each of these moves a result by a few float32 ulps, far inside the
 // tolerances the results are held to (1e-5 for float32 outputs).
-#include "common.cuh"
+#include <map>
+#include <mutex>
+#include <tuple>
+
+#include "sm100.cuh"
 
 namespace enc {
 namespace {
@@ -62,31 +66,15 @@ template <typename T, int V> union RowRegs {
     __device__ RowRegs() {}
 };
 
-template <typename T, int V, bool VEC, int OP>
-__global__ void __launch_bounds__(512) row_kernel(RowArgs a) {
+// Statistics and output of one row held in `x`.  WB = true: weight/bias vectors are already in the
+// registers `wreg`/`breg` (persistent CTAs); otherwise they are fetched from global memory (L2-resident).
+// Every thread of the CTA must call this the same number of times (it contains CTA barriers).
+template <typename T, int V, bool VEC, int OP, bool WB>
+__device__ __forceinline__ void process_row(const RowRegs<T, V> &x, const RowArgs &a, int tpr, int t, int64_t row,
+                                            bool live, float *red0, float *red1, const uint4 *wreg,
+                                            const uint4 *breg) {
     constexpr int NV = Pack<T>::N;
-    __shared__ float red0[MAX_WARPS], red1[MAX_WARPS];
-    const int tpr = a.tpr;
-    const int t = threadIdx.x & (tpr - 1);
-    const int64_t rows_per_cta = blockDim.x / tpr;
-    const int64_t row = (int64_t)blockIdx.x * rows_per_cta + threadIdx.x / tpr;
-    const bool live = row < a.rows;
-    const T *xr = reinterpret_cast<const T *>(a.x) + (live ? row : 0) * a.stride_x;
-    T *yr = reinterpret_cast<T *>(a.y) + (live ? row : 0) * a.stride_y;
     const float fill = OP == OP_SOFTMAX ? -INFINITY : 0.0f;
-
-    RowRegs<T, V> x;
-#pragma unroll
-    for (int j = 0; j < V; ++j) {
-        const int64_t c0 = ((int64_t)j * tpr + t) * NV;
-        if (VEC) {
-            if (c0 < a.cols) x.v[j] = ld_stream(xr + c0);
-        } else {
-#pragma unroll
-            for (int e = 0; e < NV; ++e)
-                if (c0 + e < a.cols) x.e[j * NV + e] = xr[c0 + e];
-        }
-    }
     // value (j, e) as float, `fill` beyond the row
     auto get = [&](int j, float *f) {
         const int64_t c0 = ((int64_t)j * tpr + t) * NV;
@@ -172,6 +160,7 @@ __global__ void __launch_bounds__(512) row_kernel(RowArgs a) {
     }
     if (!live) return;
 
+    T *yr = reinterpret_cast<T *>(a.y) + row * a.stride_y;
     const T *wr = reinterpret_cast<const T *>(a.w);
     const T *br = reinterpret_cast<const T *>(a.b);
 #pragma unroll
@@ -181,7 +170,10 @@ __global__ void __launch_bounds__(512) row_kernel(RowArgs a) {
         float f[NV], wv[NV], bv[NV];
         get(j, f);
         if (OP != OP_SOFTMAX) {
-            if (VEC) {
+            if (WB) {
+                Pack<T>::unpack(wreg[j], wv);
+                if (OP == OP_LAYERNORM) Pack<T>::unpack(breg[j], bv);
+            } else if (VEC) {
                 Pack<T>::unpack(__ldg(reinterpret_cast<const uint4 *>(wr + c0)), wv);
                 if (OP == OP_LAYERNORM) Pack<T>::unpack(__ldg(reinterpret_cast<const uint4 *>(br + c0)), bv);
             } else {
@@ -207,6 +199,124 @@ __global__ void __launch_bounds__(512) row_kernel(RowArgs a) {
             for (int e = 0; e < NV; ++e)
                 if (c0 + e < a.cols) yr[c0 + e] = from_f32<T>(o[e]);
         }
+    }
+}
+
+// One CTA per group of blockDim/tpr rows; the rows go straight from global memory to registers.
+template <typename T, int V, bool VEC, int OP>
+__global__ void __launch_bounds__(512) row_kernel(RowArgs a) {
+    constexpr int NV = Pack<T>::N;
+    __shared__ float red0[MAX_WARPS], red1[MAX_WARPS];
+    const int tpr = a.tpr;
+    const int t = threadIdx.x & (tpr - 1);
+    const int64_t rows_per_cta = blockDim.x / tpr;
+    const int64_t row = (int64_t)blockIdx.x * rows_per_cta + threadIdx.x / tpr;
+    const bool live = row < a.rows;
+    const T *xr = reinterpret_cast<const T *>(a.x) + (live ? row : 0) * a.stride_x;
+
+    RowRegs<T, V> x;
+#pragma unroll
+    for (int j = 0; j < V; ++j) {
+        const int64_t c0 = ((int64_t)j * tpr + t) * NV;
+        if (VEC) {
+            if (c0 < a.cols) x.v[j] = ld_stream(xr + c0);
+        } else {
+#pragma unroll
+            for (int e = 0; e < NV; ++e)
+                if (c0 + e < a.cols) x.e[j * NV + e] = xr[c0 + e];
+        }
+    }
+    process_row<T, V, VEC, OP, false>(x, a, tpr, t, row, live, red0, red1, nullptr, nullptr);
+}
+
+// Persistent CTAs fed by the bulk-copy engine.  Each CTA owns a ring of STAGES buffers in shared
+// memory; one elected thread keeps the ring full with cp.async.bulk row copies (completion counted in
+// bytes on the stage's mbarrier), the CTA's threads pull a stage into registers, hand the buffer back,
+// and compute and store from registers.  The bytes in flight per SM are set by the ring depth, not by
+// how many registers or warps the arithmetic needs, which is what a kernel with two CTA-wide
+// reductions per row (LayerNorm) needs to stay at HBM speed.  Weight and bias stay in registers across
+// rows.  Rows must be 16-byte aligned and a whole number of 16-byte vectors (the VEC conditions).
+struct PipeArgs {
+    RowArgs r;
+    int stages;
+    unsigned *error;
+};
+
+template <typename T, int V, int OP>
+__global__ void __launch_bounds__(512, 1) row_pipe_kernel(PipeArgs p) {
+    using namespace sm100;
+    constexpr int NV = Pack<T>::N;
+    extern __shared__ __align__(128) uint8_t pipe_smem[];
+    __shared__ float red0[MAX_WARPS], red1[MAX_WARPS];
+    __shared__ uint64_t full[16];
+    const RowArgs &a = p.r;
+    const int tpr = a.tpr, S = p.stages;
+    const int t = threadIdx.x & (tpr - 1), g = threadIdx.x / tpr;
+    const int R = blockDim.x / tpr;  // rows per stage
+    const uint32_t row_bytes = (uint32_t)(a.cols * sizeof(T));
+    const int64_t nblocks = (a.rows + R - 1) / R;
+    const T *xg = reinterpret_cast<const T *>(a.x);
+
+    auto fill_stage = [&](int s, int64_t blk) {  // thread 0 only
+        const int64_t r0 = blk * R;
+        const int live_rows = a.rows - r0 < R ? (int)(a.rows - r0) : R;
+        mbar_expect_tx(&full[s], row_bytes * live_rows);
+        for (int i = 0; i < live_rows; ++i) {
+            const uint32_t dst = smem_u32(pipe_smem + ((size_t)s * R + i) * row_bytes);
+            asm volatile("cp.async.bulk.shared::cta.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                         ::"r"(dst), "l"(xg + (r0 + i) * a.stride_x), "r"(row_bytes), "r"(smem_u32(&full[s])) : "memory");
+        }
+    };
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < S; ++s) mbar_init(&full[s], 1);
+        fence_barrier_init();
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < S; ++s) {
+            const int64_t blk = blockIdx.x + (int64_t)s * gridDim.x;
+            if (blk < nblocks) fill_stage(s, blk);
+        }
+    }
+    // weight / bias for this thread's columns, kept for every row
+    uint4 wreg[V], breg[V];
+#pragma unroll
+    for (int j = 0; j < V; ++j) {
+        const int64_t c0 = ((int64_t)j * tpr + t) * NV;
+        wreg[j] = breg[j] = make_uint4(0, 0, 0, 0);
+        if (OP != OP_SOFTMAX && c0 < a.cols) {
+            wreg[j] = __ldg(reinterpret_cast<const uint4 *>(reinterpret_cast<const T *>(a.w) + c0));
+            if (OP == OP_LAYERNORM) breg[j] = __ldg(reinterpret_cast<const uint4 *>(reinterpret_cast<const T *>(a.b) + c0));
+        }
+    }
+
+    int s = 0;
+    uint32_t parity = 0;
+    for (int64_t blk = blockIdx.x; blk < nblocks; blk += gridDim.x) {
+        // bounded wait for the stage; on expiry raise the error word and carry on with what is there
+        bool ready = false;
+        for (uint32_t i = 0; i < (1u << 20) && !ready; ++i) ready = mbar_try_wait(&full[s], parity);
+        if (!ready) atomicExch(p.error, 3u);
+        const int64_t row = blk * R + g;
+        const bool live = row < a.rows;
+        RowRegs<T, V> x;
+        const uint8_t *src = pipe_smem + ((size_t)s * R + g) * row_bytes;
+#pragma unroll
+        for (int j = 0; j < V; ++j) {
+            const int64_t c0 = ((int64_t)j * tpr + t) * NV;
+            if (c0 < a.cols) x.v[j] = *reinterpret_cast<const uint4 *>(src + c0 * sizeof(T));
+        }
+        __syncthreads();  // every thread has taken its part of the stage
+        if (threadIdx.x == 0) {
+            const int64_t next = blk + (int64_t)S * gridDim.x;
+            if (next < nblocks) {
+                fence_proxy_async();  // order the reads above before the bulk copy overwrites the buffer
+                fill_stage(s, next);
+            }
+        }
+        process_row<T, V, true, OP, true>(x, a, tpr, t, live ? row : 0, live, red0, red1, wreg, breg);
+        if (++s == S) { s = 0; parity ^= 1; }
     }
 }
 
@@ -271,10 +381,63 @@ __global__ void __launch_bounds__(1024) row_kernel_wide(RowArgs a) {
     }
 }
 
-// variant v: threads-per-row = base << (v / 3) for v / 3 in 0..3, CTA threads = {128, 256, 512}[v % 3];
-// base = fewest threads whose registers hold the row (min 32)
-constexpr int ROW_VARIANTS = 12;
-constexpr int kAutoVariant = 6;  // threads-per-row = base * 4, 128-thread CTAs
+// variant v: u = v % 12 gives threads-per-row = base << (u / 3) for u / 3 in 0..3 and CTA threads =
+// {128, 256, 512}[u % 3], where base = fewest threads whose registers hold the row (min 32);
+// v / 12 = 0: rows loaded straight into registers, 1: persistent CTAs fed by a bulk-copy ring.
+constexpr int ROW_VARIANTS = 24;
+constexpr int kAutoVariant = 3;  // threads-per-row = base * 2, 128-thread CTAs, direct loads
+
+template <typename T, int V, int OP>
+int launch_pipe(const RowArgs &a, int cta, cudaStream_t st, const char *name) {
+    PipeArgs p{a, 2, device_error_word()};
+    if (!p.error) return fail(ENC_ERR_NO_MEMORY, "%s: cannot allocate the device status word", name);
+    const int R = cta / a.tpr;
+    const size_t stage_bytes = (size_t)R * a.cols * sizeof(T);
+    const size_t budget = cta <= 128 ? 48 * 1024 : (cta <= 256 ? 64 * 1024 : 96 * 1024);
+    int stages = (int)(budget / stage_bytes);
+    if (stages < 2) stages = 2;
+    if (stages > 16) stages = 16;
+    p.stages = stages;
+    const size_t smem = stage_bytes * stages;
+    auto kern = row_pipe_kernel<T, V, OP>;
+    static std::mutex mu;
+    static std::map<std::tuple<const void *, int, size_t, int>, int> occupancy;  // per device too
+    int dev = 0;
+    cudaGetDevice(&dev);
+    int per_sm = 0;
+    {
+        std::lock_guard<std::mutex> lock(mu);
+        auto key = std::make_tuple((const void *)kern, cta, smem, dev);
+        auto it = occupancy.find(key);
+        if (it == occupancy.end()) {
+            cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+            if (e == cudaSuccess) e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, cta, smem);
+            if (e != cudaSuccess || per_sm < 1) {
+                cudaGetLastError();
+                return fail(ENC_ERR_UNSUPPORTED, "%s: the bulk-copy variant does not fit (%zu bytes of shared memory per CTA)", name, smem);
+            }
+            occupancy[key] = per_sm;
+        } else {
+            per_sm = it->second;
+        }
+    }
+    const int64_t nblocks = cdiv(a.rows, R);
+    int64_t grid = (int64_t)device_props().sm_count * per_sm;
+    if (grid > nblocks) grid = nblocks;
+    kern<<<(unsigned)grid, cta, smem, st>>>(p);
+    return check_launch(name);
+}
+
+template <typename T, int OP>
+int launch_pipe_v(const RowArgs &a, int v, int cta, cudaStream_t st, const char *name) {
+    switch (v) {
+        case 1: return launch_pipe<T, 1, OP>(a, cta, st, name);
+        case 2: return launch_pipe<T, 2, OP>(a, cta, st, name);
+        case 4: return launch_pipe<T, 4, OP>(a, cta, st, name);
+        case 8: return launch_pipe<T, 8, OP>(a, cta, st, name);
+        default: return fail(ENC_ERR_UNSUPPORTED, "%s: the bulk-copy variant holds at most 8 vectors per thread", name);
+    }
+}
 
 template <typename T, int OP, bool VEC>
 int launch_v(const RowArgs &a, int v, int cta, cudaStream_t st) {
@@ -305,7 +468,8 @@ int launch_rows(RowArgs a, int variant, cudaStream_t st, const char *name) {
     if (a.rows > 0x7fffffffLL) return fail(ENC_ERR_UNSUPPORTED, "%s: more than 2^31-1 rows", name);
     if (variant >= ROW_VARIANTS) return fail(ENC_ERR_BAD_ARG, "%s: variant %d out of range", name, variant);
     if (variant < 0) variant = kAutoVariant;
-    const int shift = variant / 3;
+    const bool pipe = variant >= 12;
+    const int shift = (variant % 12) / 3;
     int cta = 128 << (variant % 3);
     int64_t tpr64 = next_pow2(cdiv(a.cols, (int64_t)NV * MAXV));
     if (tpr64 < 32) tpr64 = 32;
@@ -323,6 +487,7 @@ int launch_rows(RowArgs a, int variant, cudaStream_t st, const char *name) {
     const bool vec = a.cols % NV == 0 && a.stride_x % NV == 0 && a.stride_y % NV == 0 &&
                      aligned16(a.x) && aligned16(a.y) &&
                      (OP == OP_SOFTMAX || aligned16(a.w)) && (OP != OP_LAYERNORM || aligned16(a.b));
+    if (pipe && vec && v <= 8) return launch_pipe_v<T, OP>(a, v, cta, st, name);
     int rc = vec ? launch_v<T, OP, true>(a, v, cta, st) : launch_v<T, OP, false>(a, v, cta, st);
     if (rc != ENC_OK) return rc;
     return check_launch(name);
@@ -344,8 +509,8 @@ template <int OP> int dispatch(const RowArgs &a, int dtype, int variant, void *s
 
 int row_variants() { return ROW_VARIANTS; }
 void row_variant_info(int v, char *out, size_t n) {
-    snprintf(out, n, "threads_per_row=base*%d cta_threads=%d (base = fewest threads whose registers hold the row, min 32)",
-             1 << (v / 3), 128 << (v % 3));
+    snprintf(out, n, "threads_per_row=base*%d cta_threads=%d %s (base = fewest threads whose registers hold the row, min 32)",
+             1 << ((v % 12) / 3), 128 << (v % 3), v >= 12 ? "persistent CTAs fed by a cp.async.bulk ring" : "direct loads");
 }
 
 }  // namespace enc

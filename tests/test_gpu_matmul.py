@@ -85,9 +85,12 @@ def test_matmul_config3_rows_sampled(oracle):
     rows = np.random.default_rng(3).choice(m, 48, replace=False)
     want = oracle.matmul_bias_gelu(host(a[rows]), host(b), host(bias), bk=64)
     assert_close(host(c[rows]), want)
-    # plain product: (2A) @ B == 2 (A @ B) exactly in floating point (scaling by two is exact)
+    # plain product: (2A) @ B == 2 (A @ B) exactly wherever the float16 result is a normal number
+    # (scaling by two is exact in the float32 accumulator and in every normal float16)
     p1, p2 = ops.matmul_desc(a, b), ops.matmul_desc(a * 2, b)
-    assert torch.equal(p2, p1 * 2)
+    normal = p1.abs() > 2.0**-13
+    assert torch.equal(p2[normal], (p1 * 2)[normal])
+    assert float(normal.float().mean()) > 0.9
     enceladus.synchronize()
 
 
