@@ -41,7 +41,18 @@ struct AttnArgs {
     int causal;
     int is_bf16;
     unsigned *error;
+#ifdef ENC_ATTN_PROF
+    unsigned long long *prof;  // [16] cycle counters summed over CTAs (debug builds only)
+#endif
 };
+
+#ifdef ENC_ATTN_PROF
+#define PROF_T0() long long t_prof = clock64()
+#define PROF_ADD(i) do { long long t_now = clock64(); if (a.prof && lane == 0) atomicAdd(a.prof + (i), (unsigned long long)(t_now - t_prof)); t_prof = t_now; } while (0)
+#else
+#define PROF_T0() do {} while (0)
+#define PROF_ADD(i) do {} while (0)
+#endif
 
 template <int D, int STAGES> struct AttnSmem {
     static constexpr int TILE = BM * D * 2;          // one 128-row block of Q, K or V
@@ -161,14 +172,19 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
                 return true;
             };
             if (ok && nkv > 0) ok = issue_s(0);
+            PROF_T0();
             for (int j = 0; j < nkv && ok; ++j) {
                 if (j + 1 < nkv) {
                     ok = issue_s(j + 1);
                     if (!ok) break;
                 }
+                PROF_ADD(8);
                 uint32_t stage, phase;
                 slot(2 * j + 1, stage, phase);
-                ok = mbar_wait(&kv_full[stage], phase, abort) && mbar_wait(p_full, j & 1, abort);
+                ok = mbar_wait(&kv_full[stage], phase, abort);
+                PROF_ADD(9);
+                ok = ok && mbar_wait(p_full, j & 1, abort);
+                PROF_ADD(10);
                 if (!ok) break;
                 tc_fence_after();
                 const uint32_t sv = smem_u32(smem + L::KV_OFF + stage * L::TILE);
@@ -181,6 +197,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
                 }
                 tc_commit(&kv_empty[stage]);
                 tc_commit(p_empty);
+                PROF_ADD(11);
             }
             if (ok) tc_commit(o_full);
         }
@@ -193,30 +210,40 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
         uint8_t *p_row = smem + L::P_OFF + r * 128;
         float m_ref = -INFINITY, l = 0.0f;
         bool ok = true;
+        PROF_T0();
         for (int j = 0; j < nkv && ok; ++j) {
             ok = mbar_wait(&s_full[j & 1], (j >> 1) & 1, abort);
             if (!ok) break;
             tc_fence_after();
+            if (warp == 2) PROF_ADD(0);
             const uint32_t t_s = tmem_base + lane_addr + S_COL + (j & 1) * BN;
             const int64_t n0 = (int64_t)j * BN;
             const bool need_mask = (n0 + BN > a.seq) || (a.causal && n0 + BN > m0);
-            // pass 1: row maximum of the scaled, masked scores
-            float mx = -INFINITY;
-#pragma unroll 1
-            for (int c0 = 0; c0 < BN; c0 += 32) {
-                uint32_t v[32];
-                tmem_ld_32x32(t_s + c0, v);
-                tmem_ld_wait();
+            // The whole score row (128 float32) comes into registers with one wait: a TMEM load issued
+            // while MMAs are in flight takes on the order of a thousand cycles, so it is paid once per block.
+            uint32_t sv[4][32];
 #pragma unroll
-                for (int i = 0; i < 32; ++i) {
-                    float s = __uint_as_float(v[i]) * a.qk_scale;
-                    if (need_mask) {
-                        const int64_t col = n0 + c0 + i;
-                        if (col >= a.seq || (a.causal && col > row)) s = -INFINITY;
+            for (int c = 0; c < 4; ++c) tmem_ld_32x32(t_s + c * 32, sv[c]);
+            tmem_ld_wait();
+            tc_fence_before();
+            mbar_arrive(&s_empty[j & 1]);  // S(j) is in registers: the buffer can take S(j+2)
+            if (warp == 2) PROF_ADD(1);
+            if (need_mask) {
+#pragma unroll
+                for (int c = 0; c < 4; ++c)
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) {
+                        const int64_t col = n0 + c * 32 + i;
+                        if (col >= a.seq || (a.causal && col > row)) sv[c][i] = __float_as_uint(-INFINITY);
                     }
-                    mx = fmaxf(mx, s);
-                }
             }
+            // row maximum of the raw scores (the scale is positive, so it commutes with the maximum)
+            float mx = -INFINITY;
+#pragma unroll
+            for (int c = 0; c < 4; ++c)
+#pragma unroll
+                for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(sv[c][i]));
+            mx *= a.qk_scale;
             const float m_new = fmaxf(m_ref, mx);
             // rescale only when the maximum moved far enough for exp2(s - m_ref) to risk overflow
             const bool rescale = m_new > m_ref + RESCALE_THRESHOLD;  // also true for the first finite maximum
@@ -225,10 +252,24 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
                 alpha = m_ref == -INFINITY ? 0.0f : fast_exp2(m_ref - m_new);
                 m_ref = m_new;
             }
+            // p = 2^(s*scale - m_ref) in place, row sum in float32
+            const float neg_m = m_ref == -INFINITY ? 0.0f : -m_ref;
+            float sum = 0.0f;
+#pragma unroll
+            for (int c = 0; c < 4; ++c)
+#pragma unroll
+                for (int i = 0; i < 32; ++i) {
+                    const float pv = fast_exp2(fmaf(__uint_as_float(sv[c][i]), a.qk_scale, neg_m));
+                    sum += pv;
+                    sv[c][i] = __float_as_uint(pv);
+                }
+            l = l * alpha + sum;
+            if (warp == 2) PROF_ADD(2);
             // P(j-1) V has finished: the P buffer is free and O is quiescent
             ok = mbar_wait(p_empty, (j & 1) ^ 1, abort);
             if (!ok) break;
             tc_fence_after();
+            if (warp == 2) PROF_ADD(3);
             if (j > 0 && __any_sync(0xffffffffu, rescale)) {
 #pragma unroll 1
                 for (int c0 = 0; c0 < D; c0 += 32) {
@@ -240,40 +281,25 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
                     tmem_st_32x32(tmem_base + lane_addr + O_COL + c0, v);
                 }
                 tmem_st_wait();
+                tc_fence_before();
             }
-            l *= alpha;
-            // pass 2: p = 2^(s - m_ref), row sum in float32, P rounded to the input type into shared memory
-            const float neg_m = m_ref == -INFINITY ? 0.0f : -m_ref;
-            float sum = 0.0f;
-#pragma unroll 1
-            for (int c0 = 0; c0 < BN; c0 += 32) {
-                uint32_t v[32];
-                tmem_ld_32x32(t_s + c0, v);
-                tmem_ld_wait();
-                float p[32];
+            // P rounded to the input type into shared memory, in the swizzled K-major layout the MMA reads:
+            // 64-wide boxes, 128-byte rows, 16-byte chunk index XOR (row & 7)
 #pragma unroll
-                for (int i = 0; i < 32; ++i) {
-                    float s = fmaf(__uint_as_float(v[i]), a.qk_scale, neg_m);
-                    if (need_mask) {
-                        const int64_t col = n0 + c0 + i;
-                        if (col >= a.seq || (a.causal && col > row)) s = -INFINITY;
-                    }
-                    p[i] = fast_exp2(s);
-                    sum += p[i];
-                }
-                // 32 columns = four 16-byte chunks of this row inside the 64-wide box (c0 / 64)
-                uint8_t *box = p_row + (c0 >> 6) * (BM * 128);
+            for (int c = 0; c < 4; ++c) {
+                uint8_t *box = p_row + (c >> 1) * (BM * 128);
 #pragma unroll
                 for (int q4 = 0; q4 < 4; ++q4) {
-                    const int chunk = ((c0 & 63) >> 3) + q4;
-                    *reinterpret_cast<uint4 *>(box + ((chunk ^ (r & 7)) << 4)) = Pack<T>::pack(p + 8 * q4);
+                    const int chunk = (c & 1) * 4 + q4;
+                    float pf[8];
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) pf[i] = __uint_as_float(sv[c][q4 * 8 + i]);
+                    *reinterpret_cast<uint4 *>(box + ((chunk ^ (r & 7)) << 4)) = Pack<T>::pack(pf);
                 }
             }
-            l += sum;
-            tc_fence_before();
-            mbar_arrive(&s_empty[j & 1]);  // this thread is done reading S(j)
-            fence_proxy_async();           // make the P stores visible to the tensor core
+            fence_proxy_async();  // make the P stores visible to the tensor core
             mbar_arrive(p_full);
+            if (warp == 2) PROF_ADD(4);
         }
         // ---- epilogue: O / l ----
         if (ok && nkv > 0) ok = mbar_wait(o_full, 0, abort);
@@ -412,8 +438,25 @@ int launch_tc(const void *q, const void *k, const void *v, const AttnArgs &args,
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return fail(ENC_ERR_LAUNCH, "enc_attention_fwd: cannot opt in to %d bytes of shared memory: %s", smem, cudaGetErrorString(e));
     dim3 grid((unsigned)cdiv(args.seq, BM), (unsigned)bh);
+#ifdef ENC_ATTN_PROF
+    AttnArgs pa = args;
+    cudaMallocManaged(&pa.prof, 16 * 8);
+    memset(pa.prof, 0, 16 * 8);
+    kern<<<grid, kThreads, smem, st>>>(tq, tk, tv, pa);
+    cudaDeviceSynchronize();
+    {
+        const double blocks = (double)grid.x * grid.y * (double)cdiv(args.seq, BN) * (args.causal ? 0.5 : 1.0);
+        const char *names[12] = {"sm wait s_full", "sm load S", "sm max+exp", "sm wait p_empty", "sm rescale+store P", "", "", "",
+                                 "mma issue_s(j+1)", "mma wait V", "mma wait p_full", "mma issue PV"};
+        for (int i = 0; i < 12; ++i)
+            if (names[i][0]) printf("  prof %-20s %9.0f cycles per kv block\n", names[i], (double)pa.prof[i] / blocks);
+    }
+    cudaFree(pa.prof);
+    return check_launch("enc_attention_fwd");
+#else
     kern<<<grid, kThreads, smem, st>>>(tq, tk, tv, args);
     return check_launch("enc_attention_fwd");
+#endif
 }
 
 template <typename T>

@@ -10,7 +10,11 @@
 //
 // The bin index is computed exactly as the reference does, in float32:
 //   b = floor((float(x) - lo) * inv_width) -> int32 (saturating, NaN -> 0); counted iff 0 <= b < bins.
-// Integer addition commutes, so the counts are bit-exact whatever the order.
+// Integer addition commutes, so the counts are bit-exact whatever the order.  The kernel is
+// instruction-issue bound before it is atomics bound, so the per-element path is kept to a handful of
+// instructions (one unsigned range compare, one address computation, one shared atomic).
+#include <type_traits>
+
 #include "common.cuh"
 
 namespace enc {
@@ -43,7 +47,11 @@ template <> struct Elems<int> {
     }
 };
 
-template <typename T, int UNROLL, bool AGGREGATE>
+// IDENTITY: int32 input with lo == 0 and inv_width == 1, where floor((float(x) - 0) * 1) == x for every
+// x that can land in a bin (bins <= 2^24, so the int -> float conversion is exact there and monotone
+// elsewhere); the bin is the value itself and the float pipeline is skipped.  Same counts, fewer
+// instructions: at HBM speed an int32 element has a budget of about twenty lane-instructions.
+template <typename T, int UNROLL, bool IDENTITY>
 __global__ void __launch_bounds__(1024) hist_kernel(HistArgs a) {
     extern __shared__ int sh[];
     constexpr int NV = Elems<T>::N;
@@ -52,54 +60,48 @@ __global__ void __launch_bounds__(1024) hist_kernel(HistArgs a) {
     for (int i = threadIdx.x; i < total; i += blockDim.x) sh[i] = 0;
     __syncthreads();
 
+    const int rshift = a.rshift;
     const int rep = threadIdx.x & (R - 1);
+    const unsigned nbins = (unsigned)a.num_bins;
+    const float lo = a.lo, inv_width = a.inv_width;
     const T *x = reinterpret_cast<const T *>(a.x);
     // The base pointer may be unaligned: peel scalar elements up to the first 16-byte boundary.
     int64_t head = (int64_t)(((16 - (reinterpret_cast<uintptr_t>(x) & 15)) & 15) / sizeof(T));
     if (head > a.n) head = a.n;
     const int64_t nvec = (a.n - head) / NV;
-    const T *xv = x + head;
+    const uint4 *xv = reinterpret_cast<const uint4 *>(x + head);
     const int64_t stride = (int64_t)gridDim.x * blockDim.x;
     const int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
 
-    // Every lane of a warp calls count() the same number of times (`valid` masks the ragged end),
-    // so the warp-wide match below always runs converged.
-    auto count = [&](float xf, bool valid) {
-        const int b = bin_of(xf, a.lo, a.inv_width);
-        const bool ok = valid && b >= 0 && b < a.num_bins;
-        if (AGGREGATE) {
-            // Lanes with the same bin elect one leader that adds the group's size: one atomic per
-            // distinct bin per warp, which pays when one bin dominates (Zipf head).
-            const unsigned peers = __match_any_sync(0xffffffffu, ok ? b : -1);
-            if (ok && (__ffs(peers) - 1) == (int)(threadIdx.x & 31))
-                atomicAdd(&sh[(b << a.rshift) + rep], __popc(peers));
-        } else if (ok) {
-            atomicAdd(&sh[(b << a.rshift) + rep], 1);
+    auto count_bin = [&](int b) {
+        if ((unsigned)b < nbins) atomicAdd(&sh[(b << rshift) + rep], 1);  // one unsigned compare covers b < 0
+    };
+    auto count_vec = [&](const uint4 &raw) {
+        if (IDENTITY) {
+            count_bin((int)raw.x); count_bin((int)raw.y); count_bin((int)raw.z); count_bin((int)raw.w);
+        } else {
+            float f[NV];
+            Elems<T>::get(raw, f);
+#pragma unroll
+            for (int e = 0; e < NV; ++e) count_bin(bin_of(f[e], lo, inv_width));
         }
     };
 
-    const int64_t iters = (nvec + stride * UNROLL - 1) / (stride * UNROLL);
-    for (int64_t it = 0; it < iters; ++it) {
-        const int64_t v0 = tid + it * stride * UNROLL;
+    for (int64_t v0 = tid; v0 < nvec; v0 += stride * UNROLL) {
         uint4 raw[UNROLL];
 #pragma unroll
         for (int u = 0; u < UNROLL; ++u)
-            raw[u] = (v0 + u * stride < nvec) ? ld_stream(xv + (v0 + u * stride) * NV) : make_uint4(0, 0, 0, 0);
+            if (v0 + u * stride < nvec) raw[u] = ld_stream(xv + v0 + u * stride);
 #pragma unroll
-        for (int u = 0; u < UNROLL; ++u) {
-            const bool valid = v0 + u * stride < nvec;
-            float f[NV];
-            Elems<T>::get(raw[u], f);
-#pragma unroll
-            for (int e = 0; e < NV; ++e) count(f[e], valid);
-        }
+        for (int u = 0; u < UNROLL; ++u)
+            if (v0 + u * stride < nvec) count_vec(raw[u]);
     }
     // scalar head and tail (each shorter than one vector)
     if (blockIdx.x == 0 && threadIdx.x < 32) {
         const int64_t tail0 = head + nvec * NV;
         const int lane = threadIdx.x;
-        count(lane < head ? to_f32(x[lane]) : 0.0f, lane < head);
-        count(tail0 + lane < a.n ? to_f32(x[tail0 + lane]) : 0.0f, tail0 + lane < a.n);
+        if (lane < head) count_bin(bin_of(to_f32(x[lane]), lo, inv_width));
+        if (tail0 + lane < a.n) count_bin(bin_of(to_f32(x[tail0 + lane]), lo, inv_width));
     }
 
     __syncthreads();
@@ -121,7 +123,7 @@ __global__ void __launch_bounds__(256) hist_global_kernel(const T *x, int *hist,
     }
 }
 
-// variant v: cta_threads = {1024, 512}[v & 1], aggregate equal bins in a warp = (v >> 1) & 1,
+// variant v: cta_threads = {1024, 512}[v & 1], vectors in flight per thread = {4, 2}[(v >> 1) & 1],
 // resident CTAs per SM = {2048/threads, half of that}[(v >> 2) & 1] (fewer CTAs = more replicas each)
 constexpr int HIST_VARIANTS = 8;
 constexpr int kMaxSmem = 200 * 1024;
@@ -137,7 +139,7 @@ int launch_hist(HistArgs a, int variant, cudaStream_t st) {
     }
     const int v = variant < 0 ? 0 : variant;
     const int threads = (v & 1) ? 512 : 1024;
-    const bool aggregate = (v >> 1) & 1;
+    const bool unroll2 = (v >> 1) & 1;
     int ctas_per_sm = (2048 / threads) >> ((v >> 2) & 1);
     const int budget = kMaxSmem / ctas_per_sm;
     int rshift = 5;
@@ -147,7 +149,13 @@ int launch_hist(HistArgs a, int variant, cudaStream_t st) {
     int64_t g = (int64_t)dp.sm_count * ctas_per_sm;
     const int64_t need = cdiv(a.n, (int64_t)threads * Elems<T>::N);
     if (g > need) g = need > 0 ? need : 1;
-    auto kern = aggregate ? hist_kernel<T, 4, true> : hist_kernel<T, 4, false>;
+    // the bin is the value itself: int32 input, unit-width bins starting at zero
+    const bool identity = std::is_same<T, int>::value && a.lo == 0.0f && a.inv_width == 1.0f && a.num_bins <= (1 << 24);
+    void (*kern)(HistArgs) = nullptr;
+    if constexpr (std::is_same<T, int>::value) {
+        if (identity) kern = unroll2 ? hist_kernel<T, 2, true> : hist_kernel<T, 4, true>;
+    }
+    if (!kern) kern = unroll2 ? hist_kernel<T, 2, false> : hist_kernel<T, 4, false>;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxSmem);
     if (e != cudaSuccess) return fail(ENC_ERR_LAUNCH, "enc_histogram: cannot opt in to %d bytes of shared memory: %s", kMaxSmem, cudaGetErrorString(e));
     kern<<<(unsigned)g, threads, smem, st>>>(a);
@@ -159,8 +167,8 @@ int launch_hist(HistArgs a, int variant, cudaStream_t st) {
 int hist_variants() { return HIST_VARIANTS; }
 void hist_variant_info(int v, char *out, size_t n) {
     const int threads = (v & 1) ? 512 : 1024;
-    snprintf(out, n, "cta_threads=%d warp_aggregate=%d ctas_per_sm=%d (replicas = largest power of two that fits, max 32)",
-             threads, (v >> 1) & 1, (2048 / threads) >> ((v >> 2) & 1));
+    snprintf(out, n, "cta_threads=%d vectors_in_flight=%d ctas_per_sm=%d (replicas = largest power of two that fits, max 32)",
+             threads, (v >> 1) & 1 ? 2 : 4, (2048 / threads) >> ((v >> 2) & 1));
 }
 
 }  // namespace enc
