@@ -59,6 +59,7 @@ SIGNATURES: dict[str, list] = {
     "enc_add": [_p, _p, _p, _i64, _i, _i, _p],
     "enc_histogram": [_p, _p, _i64, _f, _f, _i64, _i, _i, _p],
     "enc_cumsum": [_p, _p, _i64, _i64, _i64, _i64, _i, _i, _p, _i, _p],
+    "enc_cumsum_noalloc": [_p, _p, _i64, _i, _p, _p, _p],
     "enc_cumsum_out_dtype": [_i],
     "enc_sum": [_p, _p, _i64, _i, _p],
     "enc_matmul": [_p, _p, _p, _p, _i64, _i64, _i64, _i64, _i64, _i64, _i, _i, _i, _p],

@@ -478,6 +478,65 @@ int launch_sum(const void *in, void *total, int64_t n, void *stream) {
     return check_launch("enc_sum");
 }
 
+// ---- flat scan without any allocation ------------------------------------------------------------
+// Some hosts of this library must not allocate device memory when they call it: a framework that has
+// handed every byte of the device to its own pool (so cudaMalloc fails or fragments it), a serving loop
+// that cannot afford the device-wide synchronisation an allocation implies, code that runs under a
+// "no allocation after start-up" rule.  For them the tile descriptors of the look-back scan live in
+// this array, which is part of the library image: every GPU that loads the library holds it (1 MiB)
+// until the process exits.  Word 0 holds the tile ticket, word 1 a spare status word, the
+// descriptors start at word 8.
+constexpr int NOALLOC_THREADS = 512;                                   // tile = 8192 elements
+constexpr int64_t NOALLOC_MAX_TILES = 131072;                          // => at most 2^30 elements
+constexpr int64_t NOALLOC_MAX_ELEMS = NOALLOC_MAX_TILES * NOALLOC_THREADS * ITEMS;
+static __device__ __align__(256) unsigned long long g_noalloc_scratch[8 + NOALLOC_MAX_TILES];
+
+// In host code `g_noalloc_scratch` is only a handle for the symbol, not a device address; the address
+// is looked up once per device (with that device current) and cached.
+std::mutex g_noalloc_mu;
+void *g_noalloc_addr[64];
+
+int noalloc_scratch_address(void **out) {
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return fail(ENC_ERR_LAUNCH, "enc_cumsum_noalloc: no current CUDA device (%s)", cudaGetErrorString(e));
+    if (dev < 0 || dev >= 64) return fail(ENC_ERR_UNSUPPORTED, "enc_cumsum_noalloc: device ordinal %d", dev);
+    std::lock_guard<std::mutex> lock(g_noalloc_mu);
+    if (!g_noalloc_addr[dev]) {
+        void *p = nullptr;
+        e = cudaGetSymbolAddress(&p, g_noalloc_scratch);
+        if (e != cudaSuccess || !p) {
+            cudaGetLastError();
+            return fail(ENC_ERR_LAUNCH, "enc_cumsum_noalloc: cudaGetSymbolAddress failed on device %d: %s", dev, cudaGetErrorString(e));
+        }
+        g_noalloc_addr[dev] = p;
+    }
+    *out = g_noalloc_addr[dev];
+    return ENC_OK;
+}
+
+template <typename TIn>
+int launch_flat_noalloc(const void *in, void *out, int64_t n, const void *seed, unsigned *status, cudaStream_t st) {
+    using Acc = typename AccOf<TIn>::type;
+    using TOut = typename OutOf<TIn>::type;
+    constexpr int TILE = NOALLOC_THREADS * ITEMS;
+    void *base = nullptr;
+    const int rc = noalloc_scratch_address(&base);
+    if (rc != ENC_OK) return rc;
+    const int64_t ntiles = cdiv(n, TILE);
+    // The array keeps what the previous call left in it: the ticket and this call's descriptors must be zero.
+    cudaError_t e = cudaMemsetAsync(base, 0, (size_t)(8 + ntiles) * 8, st);
+    if (e != cudaSuccess) return fail(ENC_ERR_LAUNCH, "enc_cumsum_noalloc: clearing the descriptors failed: %s", cudaGetErrorString(e));
+    unsigned long long *words = reinterpret_cast<unsigned long long *>(base);
+    unsigned *spare = reinterpret_cast<unsigned *>(words + 1);
+    FlatArgs a{in, out, n, seed, words + 8, reinterpret_cast<unsigned *>(words), status ? status : spare,
+               (reinterpret_cast<uintptr_t>(in) % (4 * sizeof(TIn)) == 0 && reinterpret_cast<uintptr_t>(out) % (4 * sizeof(TOut)) == 0) ? 1 : 0};
+    int64_t grid = (int64_t)device_props().sm_count * (2048 / NOALLOC_THREADS);
+    if (grid > ntiles) grid = ntiles;
+    scan_lookback_kernel<TIn, Acc, TOut, NOALLOC_THREADS><<<(unsigned)grid, NOALLOC_THREADS, 0, st>>>(a);
+    return check_launch("enc_cumsum_noalloc");
+}
+
 }  // namespace
 
 int scan_variants() { return SCAN_VARIANTS; }
@@ -536,5 +595,34 @@ extern "C" int enc_sum(const void *in, void *total, int64_t n, int dtype, void *
         case ENC_I16: return enc::launch_sum<short>(in, total, n, stream);
         case ENC_I64: return enc::launch_sum<long long>(in, total, n, stream);
         default: return enc::fail(ENC_ERR_BAD_ARG, "enc_sum: unsupported dtype %d", dtype);
+    }
+}
+
+// Flat inclusive scan for callers that are not allowed to allocate device memory (see above).  Nothing
+// here calls cudaMalloc / cudaFree or any allocating routine: the tile descriptors live in a 1 MiB array
+// inside the library image, which caps the length at 2^30 elements.  The first call on a device looks up
+// the array's device address (cudaGetSymbolAddress); make that first call before any stream capture.
+// All calls on a device share the array, so two calls that overlap on the GPU (different streams) race;
+// calls on one stream are ordered and safe.  `status` (device pointer owned by the caller, may be NULL)
+// is set non-zero if a bounded look-back wait ran out, in which case the output is invalid.
+extern "C" int enc_cumsum_noalloc(const void *in, void *out, int64_t n, int dtype, const void *seed,
+                                  unsigned *status, void *stream) {
+    ENC_PROLOGUE();
+    if (n < 0) return enc::fail(ENC_ERR_BAD_ARG, "enc_cumsum_noalloc: negative length");
+    if (n == 0) return ENC_OK;
+    if (!in || !out) return enc::fail(ENC_ERR_BAD_ARG, "enc_cumsum_noalloc: NULL input or output");
+    if (n > enc::NOALLOC_MAX_ELEMS)
+        return enc::fail(ENC_ERR_UNSUPPORTED, "enc_cumsum_noalloc: %lld elements exceed the built-in scratch, which holds descriptors for at most %lld; use enc_cumsum",
+                         (long long)n, (long long)enc::NOALLOC_MAX_ELEMS);
+    cudaStream_t st = enc::as_stream(stream);
+    switch (dtype) {
+        case ENC_F32: return enc::launch_flat_noalloc<float>(in, out, n, seed, status, st);
+        case ENC_F16: return enc::launch_flat_noalloc<__half>(in, out, n, seed, status, st);
+        case ENC_BF16: return enc::launch_flat_noalloc<__nv_bfloat16>(in, out, n, seed, status, st);
+        case ENC_I32: return enc::launch_flat_noalloc<int>(in, out, n, seed, status, st);
+        case ENC_I8: return enc::launch_flat_noalloc<signed char>(in, out, n, seed, status, st);
+        case ENC_U8: return enc::launch_flat_noalloc<unsigned char>(in, out, n, seed, status, st);
+        case ENC_I16: return enc::launch_flat_noalloc<short>(in, out, n, seed, status, st);
+        default: return enc::fail(ENC_ERR_UNSUPPORTED, "enc_cumsum_noalloc: dtype %d (32-bit accumulators only: float32/16, bfloat16, int32/16/8, uint8)", dtype);
     }
 }

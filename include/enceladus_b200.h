@@ -152,6 +152,20 @@ int enc_cumsum(const void *in, void *out, int64_t rows, int64_t cols, int64_t st
                void *stream);
 int enc_cumsum_out_dtype(int dtype);
 
+/* The flat form of enc_cumsum (rows == 1, forward) for callers that must not allocate device memory:
+ * a framework that owns the whole device through its own pool, a serving loop that cannot take the
+ * device-wide stall of an allocation, code under a "nothing is allocated after start-up" rule.  This
+ * entry point has no counterpart in the reference.  It calls no cudaMalloc/cudaFree or other allocating
+ * routine; the look-back descriptors live in a 1 MiB array inside the library image (held by every GPU
+ * that loads the library until the process exits), which limits n to 2^30 elements — longer inputs are
+ * refused with ENC_ERR_UNSUPPORTED.  The first call on a device resolves the array's device address;
+ * make that call before any stream capture.  Every call on a device shares the array: calls on one
+ * stream are safe, calls that overlap on the GPU race.  `status` (device pointer owned by the caller, or
+ * NULL) is set non-zero if a bounded device-side wait ran out.  Same dtypes and results as enc_cumsum
+ * except ENC_I64. */
+int enc_cumsum_noalloc(const void *in, void *out, int64_t n, int dtype, const void *seed,
+                       unsigned *status, void *stream);
+
 /* total[0] = sum of n elements in the accumulator type of enc_cumsum (int32 wrap / float32).
  * Pass 1 of the multi-GPU flat scan (local total -> all-gather -> seed).  No counterpart in the
  * reference, which has no multi-device path. */
