@@ -18,7 +18,7 @@
 #include <map>
 #include <mutex>
 
-#include "common.cuh"
+#include "sm100.cuh"
 
 namespace enc {
 namespace {
@@ -272,6 +272,287 @@ __global__ void __launch_bounds__(THREADS) scan_lookback_kernel(FlatArgs a) {
     }
 }
 
+// ---- flat scan fed by a bulk-copy ring ---------------------------------------------------------
+// The look-back of a tile cannot finish before every earlier tile has been loaded and reduced, so a
+// tile that is slow to arrive stalls all the tiles behind it, and a CTA that holds its tile in
+// registers while it waits issues no new loads: with one tile per CTA the bytes in flight per SM
+// (about 100 KB of register file) are too few to ride out those stalls at HBM speed.  Here each
+// persistent CTA keeps a ring of SLOTS tiles in shared memory instead:
+//   warp 0       producer: draws tile tickets and issues one cp.async.bulk per tile into the ring
+//                (completion counted in bytes on the slot's mbarrier), as far ahead as the ring allows;
+//   warp 1       aggregator: the moment a tile lands it sums it and publishes the tile aggregate, so a
+//                claimed tile never keeps its successors waiting for longer than its own load;
+//   warp 2       resolver: obtains each tile's exclusive prefix by look-back over the predecessors'
+//                descriptors and publishes the inclusive prefix, so the L2 round trips of the look-back
+//                are off the scanners' path;
+//   warps 3..10  scanners: take the oldest resolved tile into registers (freeing its slot), scan it,
+//                add the prefix and store the result.
+// Tiles wait for their prefix in shared memory at no cost in registers, and the producer keeps the
+// memory system busy while they wait.
+constexpr int RING_SCANNERS = 256, RING_THREADS = RING_SCANNERS + 96, RING_TILE = RING_SCANNERS * ITEMS;
+
+__device__ __forceinline__ void scanner_barrier() { asm volatile("bar.sync 1, %0;" ::"n"(RING_SCANNERS) : "memory"); }
+
+// tile_scan for the 256 scanner threads of the ring kernel (named barrier 1 instead of the CTA barrier)
+template <typename Acc>
+__device__ __forceinline__ Acc ring_tile_scan(Acc (&v)[QUADS][4], Acc *sh, int tid) {
+    constexpr int NW = RING_SCANNERS / 32;
+    const int lane = tid & 31, warp = tid >> 5;
+    Acc incl[QUADS];
+#pragma unroll
+    for (int j = 0; j < QUADS; ++j) {
+        v[j][1] += v[j][0]; v[j][2] += v[j][1]; v[j][3] += v[j][2];
+        incl[j] = v[j][3];
+    }
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+#pragma unroll
+        for (int j = 0; j < QUADS; ++j) {
+            const Acc up = __shfl_up_sync(0xffffffffu, incl[j], o);
+            if (lane >= o) incl[j] += up;
+        }
+    }
+    Acc before[QUADS];
+#pragma unroll
+    for (int j = 0; j < QUADS; ++j) {
+        before[j] = __shfl_up_sync(0xffffffffu, incl[j], 1);
+        if (lane == 0) before[j] = 0;
+    }
+    scanner_barrier();  // sh may still be read by the previous tile's consumers
+    if (lane == 31) {
+#pragma unroll
+        for (int j = 0; j < QUADS; ++j) sh[j * NW + warp] = incl[j];
+    }
+    scanner_barrier();
+    if (warp == 0) {  // QUADS * NW == 32 warp totals in slab-major order: one per lane
+        const Acc mine = sh[lane];
+        Acc inc = mine;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const Acc up = __shfl_up_sync(0xffffffffu, inc, o);
+            if (lane >= o) inc += up;
+        }
+        Acc ex = __shfl_up_sync(0xffffffffu, inc, 1);
+        if (lane == 0) ex = 0;
+        sh[lane] = ex;
+        if (lane == 31) sh[QUADS * NW] = inc;
+    }
+    scanner_barrier();
+#pragma unroll
+    for (int j = 0; j < QUADS; ++j) {
+        const Acc base = sh[j * NW + warp] + before[j];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) v[j][e] += base;
+    }
+    return sh[QUADS * NW];
+}
+
+__device__ __forceinline__ bool ring_wait(uint64_t *bar, uint32_t parity, unsigned *error) {
+    for (uint32_t i = 0; i < (1u << 22); ++i)
+        if (sm100::mbar_try_wait(bar, parity)) return true;
+    atomicExch(error, 5u);
+    return false;
+}
+
+template <typename TIn, typename Acc, typename TOut>
+__global__ void __launch_bounds__(RING_THREADS) scan_ring_kernel(FlatArgs a, int slots) {
+    using namespace sm100;
+    constexpr int NW = RING_SCANNERS / 32;
+    extern __shared__ __align__(128) uint8_t ring[];
+    __shared__ uint64_t full[16], empty[16], aggd[16], pref[16];
+    __shared__ long long slot_tile[16];
+    __shared__ Acc slot_agg[16], slot_prefix[16];
+    __shared__ Acc sh[QUADS * NW + 1];
+    const TIn *in = reinterpret_cast<const TIn *>(a.in);
+    TOut *out = reinterpret_cast<TOut *>(a.out);
+    const int64_t ntiles = (a.n + RING_TILE - 1) / RING_TILE;
+    constexpr uint32_t TILE_BYTES = RING_TILE * sizeof(TIn);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < slots; ++s) {
+            mbar_init(&full[s], 1);
+            mbar_init(&aggd[s], 1);
+            mbar_init(&pref[s], 1);
+            mbar_init(&empty[s], RING_SCANNERS + 2);  // every scanner thread + aggregator + resolver
+        }
+        fence_barrier_init();
+    }
+    __syncthreads();
+
+    if (warp == 0) {
+        // ---------------- producer ----------------
+        if (lane == 0) {
+            int s = 0;
+            uint32_t parity = 1;  // a fresh slot counts as released
+            for (;;) {
+                if (!ring_wait(&empty[s], parity, a.error)) { slot_tile[s] = ntiles; mbar_arrive(&full[s]); break; }
+                const long long tile = atomicAdd(a.ticket, 1u);
+                slot_tile[s] = tile;
+                if (tile >= ntiles) {  // sentinel: tells the consumers of this CTA to stop
+                    mbar_arrive(&full[s]);
+                    break;
+                }
+                const int64_t t0 = tile * RING_TILE;
+                if (t0 + RING_TILE <= a.n) {
+                    mbar_expect_tx(&full[s], TILE_BYTES);
+                    asm volatile("cp.async.bulk.shared::cta.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                                 ::"r"(smem_u32(ring + (size_t)s * TILE_BYTES)), "l"(in + t0), "r"(TILE_BYTES), "r"(smem_u32(&full[s])) : "memory");
+                } else {
+                    mbar_arrive(&full[s]);  // ragged last tile: the consumers read it from global memory
+                }
+                if (++s == slots) { s = 0; parity ^= 1; }
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------- aggregator: tile sum, published the moment the tile has landed ----------------
+        int s = 0;
+        uint32_t parity = 0;
+        for (;;) {
+            const bool ok = ring_wait(&full[s], parity, a.error);
+            const long long tile = ok ? slot_tile[s] : ntiles;
+            if (tile >= ntiles) {
+                if (lane == 0) { slot_tile[s] = ntiles; mbar_arrive(&aggd[s]); }  // pass the sentinel on
+                break;
+            }
+            const int64_t t0 = tile * RING_TILE;
+            Acc sum = 0;
+            if (t0 + RING_TILE <= a.n) {
+                const TIn *src = reinterpret_cast<const TIn *>(ring + (size_t)s * TILE_BYTES);
+#pragma unroll 4
+                for (int q = lane; q < RING_TILE / 4; q += 32) {
+                    Acc t[4];
+                    load_quad<TIn, Acc>(src + q * 4, t);
+                    sum += (t[0] + t[1]) + (t[2] + t[3]);
+                }
+            } else {
+                for (int64_t i = t0 + lane; i < a.n; i += 32) sum += to_acc<Acc, TIn>(in[i]);
+            }
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+            if (lane == 0) {
+                if (tile == 0) {
+                    Acc seed = 0;
+                    if (a.seed) seed = *reinterpret_cast<const Acc *>(a.seed);
+                    desc_store(a.desc, FLAG_PREFIX, bits_of(Acc(seed + sum)));
+                } else {
+                    desc_store(a.desc + tile, FLAG_AGGREGATE, bits_of(sum));
+                }
+                slot_agg[s] = sum;
+                mbar_arrive(&aggd[s]);
+                mbar_arrive(&empty[s]);
+            }
+            if (++s == slots) { s = 0; parity ^= 1; }
+        }
+    } else if (warp == 2) {
+        // ---------------- resolver: exclusive prefix of each tile by look-back, off the scanners' path ----------------
+        int s = 0;
+        uint32_t parity = 0;
+        for (;;) {
+            const bool ok = ring_wait(&aggd[s], parity, a.error);
+            const long long tile = ok ? slot_tile[s] : ntiles;
+            if (tile >= ntiles) {
+                if (lane == 0) { slot_tile[s] = ntiles; mbar_arrive(&pref[s]); }
+                break;
+            }
+            Acc exclusive = 0;
+            if (tile == 0) {
+                if (a.seed) exclusive = *reinterpret_cast<const Acc *>(a.seed);
+            } else {
+                int64_t look = tile - 1;
+                bool done = false;
+                while (!done) {
+                    // two windows of 32 descriptors per round trip, nearest first
+                    unsigned long long w[2];
+#pragma unroll
+                    for (int k = 0; k < 2; ++k) {
+                        const int64_t idx = look - 32 * k - lane;
+                        w[k] = idx >= 0 ? desc_load(a.desc + idx) : ((unsigned long long)FLAG_PREFIX << 32);
+                    }
+#pragma unroll
+                    for (int k = 0; k < 2; ++k) {
+                        if (done) break;
+                        const int64_t idx = look - 32 * k - lane;
+                        unsigned flag = (unsigned)(w[k] >> 32), bits = (unsigned)w[k];
+                        unsigned spins = 0;
+                        while (flag == FLAG_EMPTY) {  // that tile has not landed yet
+                            if (++spins > SPIN_LIMIT) {
+                                atomicExch(a.error, 1u);
+                                flag = FLAG_PREFIX;
+                                bits = 0;
+                                break;
+                            }
+                            __nanosleep(40);
+                            const unsigned long long x = desc_load(a.desc + idx);
+                            flag = (unsigned)(x >> 32);
+                            bits = (unsigned)x;
+                        }
+                        const unsigned has_prefix = __ballot_sync(0xffffffffu, flag == FLAG_PREFIX);
+                        const int stop = has_prefix ? __ffs(has_prefix) - 1 : 31;
+                        Acc contrib = lane <= stop ? acc_of_bits<Acc>(bits) : Acc(0);
+#pragma unroll
+                        for (int o = 16; o > 0; o >>= 1) contrib += __shfl_xor_sync(0xffffffffu, contrib, o);
+                        exclusive += contrib;
+                        done = has_prefix != 0;
+                    }
+                    look -= 64;
+                }
+                if (lane == 0) desc_store(a.desc + tile, FLAG_PREFIX, bits_of(Acc(exclusive + slot_agg[s])));
+            }
+            if (lane == 0) {
+                slot_prefix[s] = exclusive;
+                mbar_arrive(&pref[s]);
+                mbar_arrive(&empty[s]);
+            }
+            if (++s == slots) { s = 0; parity ^= 1; }
+        }
+    } else {
+        // ---------------- scanners ----------------
+        const int tid = threadIdx.x - 96;
+        const bool vec_out = a.vec != 0;
+        int s = 0;
+        uint32_t parity = 0;
+        for (;;) {
+            if (!ring_wait(&pref[s], parity, a.error)) break;
+            const long long tile = slot_tile[s];
+            if (tile >= ntiles) break;
+            const int64_t t0 = tile * RING_TILE;
+            const bool whole = t0 + RING_TILE <= a.n;
+            const Acc prefix = slot_prefix[s];
+            Acc v[QUADS][4];
+            if (whole) {
+                const TIn *src = reinterpret_cast<const TIn *>(ring + (size_t)s * TILE_BYTES);
+#pragma unroll
+                for (int j = 0; j < QUADS; ++j) load_quad<TIn, Acc>(src + (j * RING_SCANNERS + tid) * 4, v[j]);
+            } else {
+#pragma unroll
+                for (int j = 0; j < QUADS; ++j)
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const int64_t i = t0 + ((int64_t)j * RING_SCANNERS + tid) * 4 + e;
+                        v[j][e] = i < a.n ? to_acc<Acc, TIn>(in[i]) : Acc(0);
+                    }
+            }
+            mbar_arrive(&empty[s]);  // tile and prefix are in registers: the slot can be refilled
+            ring_tile_scan<Acc>(v, sh, tid);
+#pragma unroll
+            for (int j = 0; j < QUADS; ++j) {
+                const int64_t i0 = t0 + ((int64_t)j * RING_SCANNERS + tid) * 4;
+#pragma unroll
+                for (int e = 0; e < 4; ++e) v[j][e] += prefix;
+                if (whole && vec_out) {
+                    store_quad<TOut, Acc>(out + i0, v[j]);
+                } else {
+#pragma unroll
+                    for (int e = 0; e < 4; ++e)
+                        if (i0 + e < a.n) out[i0 + e] = from_acc<TOut, Acc>(v[j][e]);
+                }
+            }
+            if (++s == slots) { s = 0; parity ^= 1; }
+        }
+    }
+}
+
 // ---- row form ------------------------------------------------------------------------------
 struct RowScanArgs {
     const void *in;
@@ -404,8 +685,38 @@ void *scratch_get(size_t bytes, void *stream) {
     return grow(s, bytes, as_stream(stream)) ? s.ptr : nullptr;
 }
 
-// variant v: CTA threads = {256, 512, 1024}[v]  (tile = threads * 16 elements)
-constexpr int SCAN_VARIANTS = 3;
+// variant v: 0..2 one tile per CTA in registers, CTA threads = {256, 512, 1024}[v] (tile = threads * 16
+// elements); 3 = 4096-element tiles through a shared-memory ring fed by the bulk-copy engine
+constexpr int SCAN_VARIANTS = 4;
+constexpr int kAutoScanVariant = 3;
+
+template <typename TIn>
+int launch_flat_ring(const void *in, void *out, int64_t n, const void *seed, cudaStream_t st, void *stream) {
+    using Acc = typename AccOf<TIn>::type;
+    using TOut = typename OutOf<TIn>::type;
+    const int64_t ntiles = cdiv(n, RING_TILE);
+    const size_t bytes = 64 + (size_t)ntiles * 8;
+    char *scr = (char *)scratch_get(bytes, stream);
+    if (!scr) return fail(ENC_ERR_NO_MEMORY, "enc_cumsum: cannot allocate %zu bytes of tile descriptors (inside a stream capture nothing can be allocated: run the same call once before capturing)", bytes);
+    unsigned *err = device_error_word();
+    if (!err) return fail(ENC_ERR_NO_MEMORY, "enc_cumsum: cannot allocate the device status word");
+    cudaError_t e = cudaMemsetAsync(scr, 0, bytes, st);
+    if (e != cudaSuccess) return fail(ENC_ERR_LAUNCH, "enc_cumsum: memset of descriptors failed: %s", cudaGetErrorString(e));
+    FlatArgs a{in, out, n, seed, (unsigned long long *)(scr + 64), (unsigned *)scr, err,
+               reinterpret_cast<uintptr_t>(out) % (4 * sizeof(TOut)) == 0 ? 1 : 0};
+    const size_t tile_bytes = (size_t)RING_TILE * sizeof(TIn);
+    int slots = (int)((96 * 1024) / tile_bytes);  // about 96 KB of tiles per CTA, two CTAs per SM
+    if (slots > 16) slots = 16;
+    if (slots < 2) slots = 2;
+    const size_t smem = tile_bytes * slots;
+    auto kern = scan_ring_kernel<TIn, Acc, TOut>;
+    e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+    if (e != cudaSuccess) return fail(ENC_ERR_LAUNCH, "enc_cumsum: cannot opt in to shared memory: %s", cudaGetErrorString(e));
+    int64_t grid = (int64_t)device_props().sm_count * 2;
+    if (grid > ntiles) grid = ntiles;
+    kern<<<(unsigned)grid, RING_THREADS, smem, st>>>(a, slots);
+    return check_launch("enc_cumsum");
+}
 
 template <typename TIn, int THREADS>
 int launch_flat_t(const void *in, void *out, int64_t n, const void *seed, cudaStream_t st, void *stream) {
@@ -446,17 +757,21 @@ int launch_scan(const void *in, void *out, int64_t rows, int64_t cols, int64_t s
     if (rows == 0 || cols == 0) return ENC_OK;
     if constexpr (LOOKBACK) {
         if (rows == 1 && !reverse) {
-            switch (variant < 0 ? 1 : variant) {
+            int v = variant < 0 ? kAutoScanVariant : variant;
+            // the bulk-copy engine needs a 16-byte aligned source; other inputs take the register kernels
+            if (v == 3 && !aligned16(in)) v = 1;
+            switch (v) {
                 case 0: return launch_flat_t<TIn, 256>(in, out, cols, seed, st, stream);
                 case 1: return launch_flat_t<TIn, 512>(in, out, cols, seed, st, stream);
-                default: return launch_flat_t<TIn, 1024>(in, out, cols, seed, st, stream);
+                case 2: return launch_flat_t<TIn, 1024>(in, out, cols, seed, st, stream);
+                default: return launch_flat_ring<TIn>(in, out, cols, seed, st, stream);
             }
         }
     }
     if (seed) return fail(ENC_ERR_UNSUPPORTED, "enc_cumsum: a seed is supported only for the forward flat form (rows == 1) of 32-bit accumulators");
     if (rows > 0x7fffffffLL) return fail(ENC_ERR_UNSUPPORTED, "enc_cumsum: more than 2^31-1 rows");
     // Short rows use small CTAs so that a row does not idle most of its threads.
-    int threads = variant < 0 ? (cols <= 4096 ? 256 : cols <= 8192 ? 512 : 1024) : (256 << variant);
+    int threads = variant < 0 || variant > 2 ? (cols <= 4096 ? 256 : cols <= 8192 ? 512 : 1024) : (256 << variant);
     switch (threads) {
         case 256: return launch_rows_t<TIn, 256>(in, out, rows, cols, si, so, reverse, st);
         case 512: return launch_rows_t<TIn, 512>(in, out, rows, cols, si, so, reverse, st);
@@ -541,7 +856,8 @@ int launch_flat_noalloc(const void *in, void *out, int64_t n, const void *seed, 
 
 int scan_variants() { return SCAN_VARIANTS; }
 void scan_variant_info(int v, char *out, size_t n) {
-    snprintf(out, n, "cta_threads=%d tile=%d elements", 256 << v, (256 << v) * ITEMS);
+    if (v == 3) snprintf(out, n, "tile=%d elements through a cp.async.bulk ring in shared memory (producer + aggregator + 256 scanner threads)", RING_TILE);
+    else snprintf(out, n, "cta_threads=%d tile=%d elements held in registers", 256 << v, (256 << v) * ITEMS);
 }
 
 void scratch_release_all() {
