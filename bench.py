@@ -405,8 +405,11 @@ def bench_workload(wl: dict, steps: int, warmup: int, pk: dict, pk_kind: str, sa
     if e2e and "run_host" in wl:
         h = pinned(wl["host"]())
         units = wl.get("host_units", wl["work"])
-        wl["run_host"](h)  # warm-up (allocator, page-locking paths)
-        wl["run_host"](h)
+        # warm-up: the launch path keeps two page-locked output buffers alive in turn (the previous
+        # result and the new one); both must exist before timing, page-locking 100+ MB takes tens of ms
+        res = None
+        for _ in range(3):
+            res = wl["run_host"](h)
         barrier()
         torch.cuda.synchronize()
         reps = 3

@@ -57,6 +57,29 @@ __device__ __forceinline__ float group_reduce(float v, int tpr, float *slot) {
     return v;
 }
 
+// Two sums at once over the threads of a row: one barrier instead of two.
+__device__ __forceinline__ void group_sum2(float &x, float &y, int tpr, float *slot_x, float *slot_y) {
+    x = warp_sum(x);
+    y = warp_sum(y);
+    if (tpr > 32) {
+        const int warp = threadIdx.x >> 5;
+        if ((threadIdx.x & 31) == 0) {
+            slot_x[warp] = x;
+            slot_y[warp] = y;
+        }
+        __syncthreads();
+        const int wpr = tpr >> 5;
+        const int first = (warp / wpr) * wpr;
+        float rx = slot_x[first], ry = slot_y[first];
+        for (int i = 1; i < wpr; ++i) {
+            rx += slot_x[first + i];
+            ry += slot_y[first + i];
+        }
+        x = rx;
+        y = ry;
+    }
+}
+
 // A row lives in registers as V raw 16-byte vectors per thread (float16/bfloat16 stay packed, which
 // halves the register cost and lets one warp hold a 4096-wide row); every pass unpacks to float32
 // on the fly.
@@ -71,7 +94,7 @@ template <typename T, int V> union RowRegs {
 // Every thread of the CTA must call this the same number of times (it contains CTA barriers).
 template <typename T, int V, bool VEC, int OP, bool WB>
 __device__ __forceinline__ void process_row(const RowRegs<T, V> &x, const RowArgs &a, int tpr, int t, int64_t row,
-                                            bool live, float *red0, float *red1, const uint4 *wreg,
+                                            bool live, float *red0, float *red1, float *red2, const uint4 *wreg,
                                             const uint4 *breg) {
     constexpr int NV = Pack<T>::N;
     const float fill = OP == OP_SOFTMAX ? -INFINITY : 0.0f;
@@ -115,30 +138,44 @@ __device__ __forceinline__ void process_row(const RowRegs<T, V> &x, const RowArg
         s0 = nm;
         s1 = __fdiv_rn(1.0f, group_reduce<false>(s, tpr, red1));
     } else if (OP == OP_LAYERNORM) {
-        float s = 0.0f;
+        // One pass gives sum and sum of squares (fill values are zero, so they do not disturb either);
+        // var = E[x^2] - mean^2 is accurate to a few ulps as long as the mean is not large against the
+        // spread.  When it is (mean^2 > 16 var: cancellation would cost more than 1e-6 of relative
+        // accuracy), the variance is recomputed from the registers in the centred form the reference
+        // uses.  The choice is made for the whole CTA because the reductions contain CTA barriers.
+        float s = 0.0f, q = 0.0f;
 #pragma unroll
         for (int j = 0; j < V; ++j) {
-            float f[NV];
-            get(j, f);
-#pragma unroll
-            for (int e = 0; e < NV; ++e) s += f[e];
-        }
-        const float n = (float)a.cols;
-        const float mean = __fdiv_rn(group_reduce<false>(s, tpr, red0), n);
-        float q = 0.0f;
-#pragma unroll
-        for (int j = 0; j < V; ++j) {
-            const int64_t c0 = ((int64_t)j * tpr + t) * NV;
-            if (VEC && c0 >= a.cols) continue;  // a vector is inside the row or entirely past it
             float f[NV];
             get(j, f);
 #pragma unroll
             for (int e = 0; e < NV; ++e) {
-                const float d = (VEC || c0 + e < a.cols) ? f[e] - mean : 0.0f;
-                q = fmaf(d, d, q);
+                s += f[e];
+                q = fmaf(f[e], f[e], q);
             }
         }
-        const float var = __fdiv_rn(group_reduce<false>(q, tpr, red1), n);
+        const float n = (float)a.cols;
+        group_sum2(s, q, tpr, red0, red1);
+        const float mean = __fdiv_rn(s, n);
+        float var = fmaf(-mean, mean, __fdiv_rn(q, n));
+        const bool ill = !(mean * mean <= 16.0f * var);  // also catches var <= 0 and NaN
+        // (a CTA that holds a single row already agrees on `ill` and needs no vote)
+        if ((int)blockDim.x == tpr ? ill : (bool)__syncthreads_or(ill)) {
+            float qc = 0.0f;
+#pragma unroll
+            for (int j = 0; j < V; ++j) {
+                const int64_t c0 = ((int64_t)j * tpr + t) * NV;
+                if (VEC && c0 >= a.cols) continue;  // a vector is inside the row or entirely past it
+                float f[NV];
+                get(j, f);
+#pragma unroll
+                for (int e = 0; e < NV; ++e) {
+                    const float d = (VEC || c0 + e < a.cols) ? f[e] - mean : 0.0f;
+                    qc = fmaf(d, d, qc);
+                }
+            }
+            var = __fdiv_rn(group_reduce<false>(qc, tpr, red2), n);
+        }
         const float rstd = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(var, a.eps)));
         s0 = rstd;
         s1 = -mean * rstd;  // (x - mean) * rstd = x*rstd - mean*rstd
@@ -206,7 +243,7 @@ __device__ __forceinline__ void process_row(const RowRegs<T, V> &x, const RowArg
 template <typename T, int V, bool VEC, int OP>
 __global__ void __launch_bounds__(512) row_kernel(RowArgs a) {
     constexpr int NV = Pack<T>::N;
-    __shared__ float red0[MAX_WARPS], red1[MAX_WARPS];
+    __shared__ float red0[MAX_WARPS], red1[MAX_WARPS], red2[MAX_WARPS];
     const int tpr = a.tpr;
     const int t = threadIdx.x & (tpr - 1);
     const int64_t rows_per_cta = blockDim.x / tpr;
@@ -226,7 +263,7 @@ __global__ void __launch_bounds__(512) row_kernel(RowArgs a) {
                 if (c0 + e < a.cols) x.e[j * NV + e] = xr[c0 + e];
         }
     }
-    process_row<T, V, VEC, OP, false>(x, a, tpr, t, row, live, red0, red1, nullptr, nullptr);
+    process_row<T, V, VEC, OP, false>(x, a, tpr, t, row, live, red0, red1, red2, nullptr, nullptr);
 }
 
 // Persistent CTAs fed by the bulk-copy engine.  Each CTA owns a ring of STAGES buffers in shared
@@ -247,7 +284,7 @@ __global__ void __launch_bounds__(512, 1) row_pipe_kernel(PipeArgs p) {
     using namespace sm100;
     constexpr int NV = Pack<T>::N;
     extern __shared__ __align__(128) uint8_t pipe_smem[];
-    __shared__ float red0[MAX_WARPS], red1[MAX_WARPS];
+    __shared__ float red0[MAX_WARPS], red1[MAX_WARPS], red2[MAX_WARPS];
     __shared__ uint64_t full[16];
     const RowArgs &a = p.r;
     const int tpr = a.tpr, S = p.stages;
@@ -315,7 +352,7 @@ __global__ void __launch_bounds__(512, 1) row_pipe_kernel(PipeArgs p) {
                 fill_stage(s, next);
             }
         }
-        process_row<T, V, true, OP, true>(x, a, tpr, t, live ? row : 0, live, red0, red1, wreg, breg);
+        process_row<T, V, true, OP, true>(x, a, tpr, t, live ? row : 0, live, red0, red1, red2, wreg, breg);
         if (++s == S) { s = 0; parity ^= 1; }
     }
 }
