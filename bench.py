@@ -42,9 +42,23 @@ FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustain
 L2_BYTES = 126 << 20
 ROTATE_BYTES = 1 << 30  # total size of the rotating buffer sets for workloads smaller than this
 
-# dram__bytes_read.sum + dram__bytes_write.sum per launch from the ncu captures summarised under
-# profiles/ (bytes); None where no capture exists yet.
-NCU_TRAFFIC: dict[str, float | None] = {}
+# dram__bytes_read.sum + dram__bytes_write.sum per launch (bytes), from the `ncu --set full` captures
+# summarised under profiles/ (one file per workload, with the capturing command).  The 2^30 / 2^28-element
+# workloads were captured at 2^27 elements (few GB on the device under the profiler) and are scaled by
+# the element count: their traffic is proportional to it.
+NCU_TRAFFIC: dict[str, float | None] = {
+    "layernorm_bf16_16384x4096": 216_871_680,       # profiles/layernorm.md
+    "rmsnorm_bf16_16384x4096": 214_638_848,         # profiles/rmsnorm.md
+    "softmax_f32_4096x1024": 16_790_272,            # profiles/softmax.md (the 16 MiB output stays in L2)
+    "gelu_tanh_f32_2p28": 2_101_770_000,            # profiles/gelu.md
+    "histogram_i32_2p30_uniform256": 8 * 541_015_552,   # profiles/hist_uniform256.md, captured at 2^27
+    "histogram_i32_2p30_zipf4096": 8 * 541_702_144,     # profiles/hist_zipf4096.md, captured at 2^27
+    "cumsum_i32_2p30": 8 * 1_020_266_240,           # profiles/cumsum_i32.md, captured at 2^27
+    "cumsum_f32_2p28": 2 * 1_020_002_560,           # profiles/cumsum_f32.md, captured at 2^27
+    "matmul_bias_gelu_f16_8192x8192x8192": 1_105_655_808,   # profiles/matmul.md
+    "attention_bf16_8x32x4096x128_full": 1_057_471_232,     # profiles/attention_full.md
+    "attention_bf16_8x32x4096x128_causal": 1_056_619_008,   # profiles/attention_causal.md
+}
 
 
 def peaks() -> tuple[dict, str]:

@@ -54,6 +54,100 @@ struct AttnArgs {
 #define PROF_ADD(i) do {} while (0)
 #endif
 
+// ---- exponentials and P rounding off the special-function unit --------------------------------------
+// A 128 x 128 score block needs 16384 exponentials and 8192 two-value conversions; at 16 results per clock
+// per SM the special-function unit would be busy for longer than the two matrix products of the block.
+// Half of the exponentials are therefore evaluated on the FMA pipes, and bfloat16 rounding is done with
+// integer adds and a byte permute instead of a conversion instruction.
+
+// 2^x for x <= ~100 without the special-function unit: x = i + f with i integer and f in [-0.5, 0.5],
+// 2^f by a cubic (max relative error 7.7e-5, below the bfloat16/float16 rounding of P), the exponent field
+// adjusted by i.  Inputs below -126 (masked scores) give 2^-126 instead of zero.
+__device__ __forceinline__ float exp2_fma(float x) {
+    x = fmaxf(x, -126.0f);
+    const float t = x + 12582912.0f;  // 1.5 * 2^23: the sum rounds x to the nearest integer in the low mantissa bits
+    const float f = x - (t - 12582912.0f);
+    float p = fmaf(f, 0.05508868396282196f, 0.24260404706001282f);
+    p = fmaf(p, f, 0.6932762265205383f);
+    p = fmaf(p, f, 0.9999289512634277f);
+    return __uint_as_float(__float_as_uint(p) + (__float_as_uint(t) << 23));
+}
+
+// eight float32 bit patterns -> eight values of the input type in 16 bytes
+template <typename T> __device__ __forceinline__ uint4 pack_p(const uint32_t *v);
+template <> __device__ __forceinline__ uint4 pack_p<__half>(const uint32_t *v) {
+    float f[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) f[i] = __uint_as_float(v[i]);
+    return Pack<__half>::pack(f);
+}
+template <> __device__ __forceinline__ uint4 pack_p<__nv_bfloat16>(const uint32_t *v) {
+    // round to nearest (ties away from zero; P is non-negative and finite): add half an ulp, keep the high halves
+    uint32_t w[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) w[i] = __byte_perm(v[2 * i] + 0x8000u, v[2 * i + 1] + 0x8000u, 0x7632);
+    return make_uint4(w[0], w[1], w[2], w[3]);
+}
+
+// One row of one score block, in registers: mask, running maximum with lazy rescale, probabilities in
+// place (float32 bit patterns), row sum.  `alpha` is the factor the accumulator must be scaled by (1 when
+// no rescale is due).
+__device__ __forceinline__ void softmax_row(uint32_t (&sv)[4][32], float qk_scale, bool need_mask, int64_t n0, int64_t row,
+                                            int64_t seq, int causal, float &m_ref, float &l, float &alpha, bool &rescale) {
+    if (need_mask) {
+#pragma unroll
+        for (int c = 0; c < 4; ++c)
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {
+                const int64_t col = n0 + c * 32 + i;
+                if (col >= seq || (causal && col > row)) sv[c][i] = __float_as_uint(-INFINITY);
+            }
+    }
+    // row maximum of the raw scores (the scale is positive, so it commutes with the maximum)
+    float mx = -INFINITY;
+#pragma unroll
+    for (int c = 0; c < 4; ++c)
+#pragma unroll
+        for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(sv[c][i]));
+    mx *= qk_scale;
+    const float m_new = fmaxf(m_ref, mx);
+    // rescale only when the maximum moved far enough for exp2(s - m_ref) to risk overflow
+    rescale = m_new > m_ref + RESCALE_THRESHOLD;  // also true for the first finite maximum
+    alpha = 1.0f;
+    if (rescale) {
+        alpha = m_ref == -INFINITY ? 0.0f : fast_exp2(m_ref - m_new);
+        m_ref = m_new;
+    }
+    const float neg_m = m_ref == -INFINITY ? 0.0f : -m_ref;
+    float sum0 = 0.0f, sum1 = 0.0f;
+#pragma unroll
+    for (int c = 0; c < 4; ++c)
+#pragma unroll
+        for (int i = 0; i < 32; i += 2) {
+            const float p0 = fast_exp2(fmaf(__uint_as_float(sv[c][i]), qk_scale, neg_m));     // special-function unit
+            const float p1 = exp2_fma(fmaf(__uint_as_float(sv[c][i + 1]), qk_scale, neg_m));  // FMA pipes
+            sum0 += p0;
+            sum1 += p1;
+            sv[c][i] = __float_as_uint(p0);
+            sv[c][i + 1] = __float_as_uint(p1);
+        }
+    l = l * alpha + (sum0 + sum1);
+}
+
+// P row into shared memory in the swizzled K-major layout the MMA reads: 64-wide boxes, 128-byte rows,
+// 16-byte chunk index XOR (row & 7).
+template <typename T> __device__ __forceinline__ void store_p_row(uint8_t *p_row, int r, const uint32_t (&sv)[4][32]) {
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+        uint8_t *box = p_row + (c >> 1) * (BM * 128);
+#pragma unroll
+        for (int q4 = 0; q4 < 4; ++q4) {
+            const int chunk = (c & 1) * 4 + q4;
+            *reinterpret_cast<uint4 *>(box + ((chunk ^ (r & 7)) << 4)) = pack_p<T>(&sv[c][q4 * 8]);
+        }
+    }
+}
+
 template <int D, int STAGES> struct AttnSmem {
     static constexpr int TILE = BM * D * 2;          // one 128-row block of Q, K or V
     static constexpr int Q_OFF = 0;
@@ -228,42 +322,9 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
             tc_fence_before();
             mbar_arrive(&s_empty[j & 1]);  // S(j) is in registers: the buffer can take S(j+2)
             if (warp == 2) PROF_ADD(1);
-            if (need_mask) {
-#pragma unroll
-                for (int c = 0; c < 4; ++c)
-#pragma unroll
-                    for (int i = 0; i < 32; ++i) {
-                        const int64_t col = n0 + c * 32 + i;
-                        if (col >= a.seq || (a.causal && col > row)) sv[c][i] = __float_as_uint(-INFINITY);
-                    }
-            }
-            // row maximum of the raw scores (the scale is positive, so it commutes with the maximum)
-            float mx = -INFINITY;
-#pragma unroll
-            for (int c = 0; c < 4; ++c)
-#pragma unroll
-                for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(sv[c][i]));
-            mx *= a.qk_scale;
-            const float m_new = fmaxf(m_ref, mx);
-            // rescale only when the maximum moved far enough for exp2(s - m_ref) to risk overflow
-            const bool rescale = m_new > m_ref + RESCALE_THRESHOLD;  // also true for the first finite maximum
-            float alpha = 1.0f;
-            if (rescale) {
-                alpha = m_ref == -INFINITY ? 0.0f : fast_exp2(m_ref - m_new);
-                m_ref = m_new;
-            }
-            // p = 2^(s*scale - m_ref) in place, row sum in float32
-            const float neg_m = m_ref == -INFINITY ? 0.0f : -m_ref;
-            float sum = 0.0f;
-#pragma unroll
-            for (int c = 0; c < 4; ++c)
-#pragma unroll
-                for (int i = 0; i < 32; ++i) {
-                    const float pv = fast_exp2(fmaf(__uint_as_float(sv[c][i]), a.qk_scale, neg_m));
-                    sum += pv;
-                    sv[c][i] = __float_as_uint(pv);
-                }
-            l = l * alpha + sum;
+            float alpha;
+            bool rescale;
+            softmax_row(sv, a.qk_scale, need_mask, n0, row, a.seq, a.causal, m_ref, l, alpha, rescale);
             if (warp == 2) PROF_ADD(2);
             // P(j-1) V has finished: the P buffer is free and O is quiescent
             ok = mbar_wait(p_empty, (j & 1) ^ 1, abort);
@@ -283,20 +344,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
                 tmem_st_wait();
                 tc_fence_before();
             }
-            // P rounded to the input type into shared memory, in the swizzled K-major layout the MMA reads:
-            // 64-wide boxes, 128-byte rows, 16-byte chunk index XOR (row & 7)
-#pragma unroll
-            for (int c = 0; c < 4; ++c) {
-                uint8_t *box = p_row + (c >> 1) * (BM * 128);
-#pragma unroll
-                for (int q4 = 0; q4 < 4; ++q4) {
-                    const int chunk = (c & 1) * 4 + q4;
-                    float pf[8];
-#pragma unroll
-                    for (int i = 0; i < 8; ++i) pf[i] = __uint_as_float(sv[c][q4 * 8 + i]);
-                    *reinterpret_cast<uint4 *>(box + ((chunk ^ (r & 7)) << 4)) = Pack<T>::pack(pf);
-                }
-            }
+            store_p_row<T>(p_row, r, sv);
             fence_proxy_async();  // make the P stores visible to the tensor core
             mbar_arrive(p_full);
             if (warp == 2) PROF_ADD(4);
@@ -316,6 +364,269 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
 #pragma unroll
                     for (int i = 0; i < 32; ++i) v[i] = 0;
                 }
+                if (row < a.seq) {
+                    float f[32];
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) f[i] = __fdiv_rn(__uint_as_float(v[i]), l);
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) *reinterpret_cast<uint4 *>(o + c0 + 8 * i) = Pack<T>::pack(f + 8 * i);
+                }
+            }
+            if (a.lse && row < a.seq) a.lse[(int64_t)bh * a.seq + row] = (m_ref + log2f(l)) * LN2;
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (threadIdx.x == 0 && *abort) atomicExch(a.error, 4u);
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, TMEM_COLS);
+    }
+}
+
+// ---- two query tiles per CTA -------------------------------------------------------------------------
+// The softmax of one 128-row tile takes longer than its two matrix products, so with a single tile per
+// CTA the tensor core idles about half of the time.  This kernel gives every CTA 256 query rows as two
+// independent 128-row tiles, each with its own softmax warpgroup, accumulator and score buffer in
+// tensor memory: while one warpgroup exponentiates, the tensor core serves the other tile, and every
+// K/V block fetched into shared memory is used twice.
+//   warpgroup 0   warp 0 = TMA producer, warp 1 = MMA issuer (registers released with setmaxnreg)
+//   warpgroup 1   softmax of tile 0          warpgroup 2   softmax of tile 1
+// TMEM columns: S0 [0,128) S1 [128,256) O0 [256,256+D) O1 [384,384+D).  Issue order per K/V block j:
+// S0(j+1), P0(j)V, S1(j+1), P1(j)V - each score product goes out as soon as the tile's softmax has pulled
+// the previous scores into registers.
+constexpr int kThreads2 = 384;
+
+template <int D, int STAGES> struct AttnSmem2 {
+    static constexpr int TILE = BM * D * 2;
+    static constexpr int Q_OFF = 0;                       // 2 query tiles
+    static constexpr int P_OFF = 2 * TILE;                // 2 probability tiles of 128 x 128
+    static constexpr int P_BYTES = BM * BN * 2;
+    static constexpr int KV_OFF = P_OFF + 2 * P_BYTES;
+    static constexpr int BAR_OFF = KV_OFF + STAGES * TILE;
+    static constexpr int NBARS = 1 + 2 * STAGES + 8 + 1;  // q, kv full/empty, (s_full, s_empty, p_full, p_empty) x 2, o
+    static constexpr int TOTAL = BAR_OFF + NBARS * 8 + 16;
+};
+
+template <typename T, int D, int STAGES>
+__global__ void __launch_bounds__(kThreads2, 1)
+attention_tc2_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
+                     const __grid_constant__ CUtensorMap tm_v, AttnArgs a) {
+    using L = AttnSmem2<D, STAGES>;
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
+    uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint64_t *q_full = reinterpret_cast<uint64_t *>(smem + L::BAR_OFF);
+    uint64_t *kv_full = q_full + 1;
+    uint64_t *kv_empty = kv_full + STAGES;
+    uint64_t *s_full = kv_empty + STAGES;  // [2] one per tile
+    uint64_t *s_empty = s_full + 2;
+    uint64_t *p_full = s_empty + 2;
+    uint64_t *p_empty = p_full + 2;
+    uint64_t *o_full = p_empty + 2;
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(o_full + 1);
+    volatile uint32_t *abort = tmem_slot + 1;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int qb = a.causal ? (int)(gridDim.x - 1 - blockIdx.x) : (int)blockIdx.x;  // heavy blocks first
+    const int bh = blockIdx.y;
+    const int64_t m0 = (int64_t)qb * (2 * BM);
+    // key blocks each tile needs: all of them, or up to its own diagonal; none for a tile past the sequence
+    int nkv_t[2];
+#pragma unroll
+    for (int t = 0; t < 2; ++t) {
+        const int64_t r0 = m0 + t * BM;
+        const int64_t hi = a.causal ? (r0 + BM < a.seq ? r0 + BM : a.seq) : a.seq;
+        nkv_t[t] = r0 < a.seq ? (int)((hi + BN - 1) / BN) : 0;
+    }
+    const int nkv = nkv_t[0] > nkv_t[1] ? nkv_t[0] : nkv_t[1];
+    constexpr uint32_t TMEM_COLS = 512;
+
+    if (threadIdx.x == 0) {
+        mbar_init(q_full, 1);
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(&kv_full[s], 1);
+            mbar_init(&kv_empty[s], 1);
+        }
+        for (int t = 0; t < 2; ++t) {
+            mbar_init(&s_full[t], 1);
+            mbar_init(&s_empty[t], 128);
+            mbar_init(&p_full[t], 128);
+            mbar_init(&p_empty[t], 1);
+        }
+        mbar_init(o_full, 1);
+        *abort = 0;
+        fence_barrier_init();
+        prefetch_tensormap(&tm_q);
+        prefetch_tensormap(&tm_k);
+        prefetch_tensormap(&tm_v);
+    }
+    if (warp == 1) tmem_alloc(tmem_slot, TMEM_COLS);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp < 4) {
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 56;");
+        if (warp == 0 && lane == 0) {
+            // ---------------- TMA producer ----------------
+            mbar_expect_tx(q_full, 2 * L::TILE);
+#pragma unroll
+            for (int t = 0; t < 2; ++t)
+#pragma unroll
+                for (int b = 0; b < D / 64; ++b)
+                    tma_load_3d(smem + L::Q_OFF + t * L::TILE + b * (BM * 128), &tm_q, q_full, b * 64, (int)(m0 + t * BM), bh);
+            bool ok = true;
+            uint32_t stage = 0, phase = 0;
+            for (int it = 0; it < 2 * nkv && ok; ++it) {  // K0 V0 K1 V1 ...
+                const int j = it >> 1;
+                ok = mbar_wait(&kv_empty[stage], phase ^ 1, abort);
+                if (!ok) break;
+                uint8_t *dst = smem + L::KV_OFF + stage * L::TILE;
+                mbar_expect_tx(&kv_full[stage], L::TILE);
+                const CUtensorMap *tm = (it & 1) ? &tm_v : &tm_k;
+#pragma unroll
+                for (int b = 0; b < D / 64; ++b) tma_load_3d(dst + b * (BN * 128), tm, &kv_full[stage], b * 64, j * BN, bh);
+                if (++stage == STAGES) { stage = 0; phase ^= 1; }
+            }
+            if (*abort) {  // drain our own copies before the CTA exits
+                for (uint32_t i = 0; i < (1u << 16) && !mbar_try_wait(q_full, 0); ++i) {}
+                for (uint32_t s = 0; s < (uint32_t)STAGES; ++s) {
+                    const uint32_t p = s < stage ? phase : phase ^ 1;
+                    for (uint32_t i = 0; i < (1u << 16) && !mbar_try_wait(&kv_full[s], p); ++i) {}
+                }
+            }
+        } else if (warp == 1 && lane == 0) {
+            // ---------------- MMA issuer ----------------
+            const uint32_t idesc_s = idesc_f16(a.is_bf16, /*b_mn_major=*/false, BM, BN);
+            const uint32_t idesc_o = idesc_f16(a.is_bf16, /*b_mn_major=*/true, BM, D);
+            bool ok = mbar_wait(q_full, 0, abort);
+            auto slot = [&](int it, uint32_t &stage, uint32_t &phase) { stage = it % STAGES; phase = (it / STAGES) & 1; };
+            auto mma_s = [&](int t, int j, uint32_t sk) -> bool {  // S_t = Q_t K_j^T
+                if (!mbar_wait(&s_empty[t], (j & 1) ^ 1, abort)) return false;
+                tc_fence_after();
+                const uint32_t sq = smem_u32(smem + L::Q_OFF + t * L::TILE);
+#pragma unroll
+                for (int kk = 0; kk < D / 16; ++kk) {
+                    const uint32_t off = (kk >> 2) * (BM * 128) + (kk & 3) * 32;
+                    tc_mma_f16(tmem_base + t * BN, smem_desc_sw128(sq + off, 16, 1024), smem_desc_sw128(sk + off, 16, 1024), idesc_s, kk != 0);
+                }
+                tc_commit(&s_full[t]);
+                return true;
+            };
+            auto mma_pv = [&](int t, int j, uint32_t sv) -> bool {  // O_t += P_t V_j
+                if (!mbar_wait(&p_full[t], j & 1, abort)) return false;
+                tc_fence_after();
+                const uint32_t sp = smem_u32(smem + L::P_OFF + t * L::P_BYTES);
+#pragma unroll
+                for (int kk = 0; kk < BN / 16; ++kk) {
+                    const uint32_t poff = (kk >> 2) * (BM * 128) + (kk & 3) * 32;
+                    tc_mma_f16(tmem_base + 256 + t * 128, smem_desc_sw128(sp + poff, 16, 1024),
+                               smem_desc_sw128(sv + kk * 2048, BN * 128, 1024), idesc_o, (j | kk) != 0);
+                }
+                tc_commit(&p_empty[t]);
+                return true;
+            };
+            uint32_t stage, phase;
+            if (ok && nkv > 0) {
+                slot(0, stage, phase);
+                ok = mbar_wait(&kv_full[stage], phase, abort);
+                const uint32_t sk = smem_u32(smem + L::KV_OFF + stage * L::TILE);
+                for (int t = 0; t < 2 && ok; ++t)
+                    if (nkv_t[t] > 0) ok = mma_s(t, 0, sk);
+                if (ok) tc_commit(&kv_empty[stage]);
+            }
+            for (int j = 0; j < nkv && ok; ++j) {
+                uint32_t kstage = 0, vstage;
+                uint32_t sk = 0;
+                const bool more = j + 1 < nkv;
+                if (more) {
+                    slot(2 * (j + 1), kstage, phase);
+                    ok = mbar_wait(&kv_full[kstage], phase, abort);
+                    if (!ok) break;
+                    sk = smem_u32(smem + L::KV_OFF + kstage * L::TILE);
+                }
+                slot(2 * j + 1, vstage, phase);
+                const uint32_t vphase = phase;
+                const uint32_t sv = smem_u32(smem + L::KV_OFF + vstage * L::TILE);
+                bool v_ready = false;
+                for (int t = 0; t < 2 && ok; ++t) {
+                    if (more && j + 1 < nkv_t[t]) ok = mma_s(t, j + 1, sk);
+                    if (ok && j < nkv_t[t]) {
+                        if (!v_ready) {
+                            ok = mbar_wait(&kv_full[vstage], vphase, abort);
+                            v_ready = true;
+                        }
+                        if (ok) ok = mma_pv(t, j, sv);
+                    }
+                }
+                if (!ok) break;
+                if (more) tc_commit(&kv_empty[kstage]);
+                tc_commit(&kv_empty[vstage]);
+            }
+            if (ok) tc_commit(o_full);
+        }
+    } else {
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 224;");
+        // ---------------- softmax warpgroups: tile = warpgroup - 1 ----------------
+        const int t = (warp >> 2) - 1;
+        const int quarter = warp & 3;
+        const int r = quarter * 32 + lane;  // row inside the tile == TMEM lane
+        const int64_t row = m0 + t * BM + r;
+        const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
+        const uint32_t t_s = tmem_base + lane_addr + t * BN;
+        const uint32_t t_o = tmem_base + lane_addr + 256 + t * 128;
+        uint8_t *p_row = smem + L::P_OFF + t * L::P_BYTES + r * 128;
+        const int my_nkv = nkv_t[t];
+        const int64_t tile_m0 = m0 + t * BM;
+        float m_ref = -INFINITY, l = 0.0f;
+        bool ok = true;
+        for (int j = 0; j < my_nkv && ok; ++j) {
+            ok = mbar_wait(&s_full[t], j & 1, abort);
+            if (!ok) break;
+            tc_fence_after();
+            const int64_t n0 = (int64_t)j * BN;
+            const bool need_mask = (n0 + BN > a.seq) || (a.causal && n0 + BN > tile_m0);
+            uint32_t sv[4][32];
+#pragma unroll
+            for (int c = 0; c < 4; ++c) tmem_ld_32x32(t_s + c * 32, sv[c]);
+            tmem_ld_wait();
+            tc_fence_before();
+            mbar_arrive(&s_empty[t]);  // S_t(j) is in registers: the buffer can take S_t(j+1)
+            float alpha;
+            bool rescale;
+            softmax_row(sv, a.qk_scale, need_mask, n0, row, a.seq, a.causal, m_ref, l, alpha, rescale);
+            ok = mbar_wait(&p_empty[t], (j & 1) ^ 1, abort);  // P_t(j-1) V done: P buffer free, O_t quiescent
+            if (!ok) break;
+            tc_fence_after();
+            if (j > 0 && __any_sync(0xffffffffu, rescale)) {
+#pragma unroll 1
+                for (int c0 = 0; c0 < D; c0 += 32) {
+                    uint32_t v[32];
+                    tmem_ld_32x32(t_o + c0, v);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * alpha);
+                    tmem_st_32x32(t_o + c0, v);
+                }
+                tmem_st_wait();
+                tc_fence_before();
+            }
+            store_p_row<T>(p_row, r, sv);
+            fence_proxy_async();
+            mbar_arrive(&p_full[t]);
+        }
+        // ---- epilogue: O_t / l ----
+        if (ok && my_nkv > 0) ok = mbar_wait(o_full, 0, abort);
+        if (ok && my_nkv > 0) {
+            tc_fence_after();
+            T *o = reinterpret_cast<T *>(a.o) + (int64_t)bh * a.stride_h + row * a.stride_m;
+#pragma unroll 1
+            for (int c0 = 0; c0 < D; c0 += 32) {
+                uint32_t v[32];
+                tmem_ld_32x32(t_o + c0, v);
+                tmem_ld_wait();
                 if (row < a.seq) {
                     float f[32];
 #pragma unroll
@@ -419,7 +730,7 @@ __global__ void __launch_bounds__(128) attention_simple_kernel(const T *q, const
     }
 }
 
-constexpr int ATTN_VARIANTS = 2;  // 0: 128x128 tiles, 4-deep K/V ring; 1: 3-deep ring
+constexpr int ATTN_VARIANTS = 3;  // 0: two 128-row query tiles per CTA; 1, 2: one tile, 4- or 3-deep K/V ring
 
 template <typename T, int D, int STAGES>
 int launch_tc(const void *q, const void *k, const void *v, const AttnArgs &args, int64_t bh, cudaStream_t st) {
@@ -459,6 +770,27 @@ int launch_tc(const void *q, const void *k, const void *v, const AttnArgs &args,
 #endif
 }
 
+template <typename T, int D, int STAGES>
+int launch_tc2(const void *q, const void *k, const void *v, const AttnArgs &args, int64_t bh, cudaStream_t st) {
+    using L = AttnSmem2<D, STAGES>;
+    char err[256];
+    CUtensorMap tq, tk, tv;
+    const uint64_t dims[3] = {(uint64_t)D, (uint64_t)args.seq, (uint64_t)bh};
+    const uint64_t strides[2] = {(uint64_t)args.stride_m * 2, (uint64_t)args.stride_h * 2};
+    const uint32_t box[3] = {64, BM, 1};
+    if (!make_tensor_map(&tq, q, args.is_bf16, 3, dims, strides, box, err, sizeof(err)) ||
+        !make_tensor_map(&tk, k, args.is_bf16, 3, dims, strides, box, err, sizeof(err)) ||
+        !make_tensor_map(&tv, v, args.is_bf16, 3, dims, strides, box, err, sizeof(err)))
+        return fail(ENC_ERR_LAUNCH, "enc_attention_fwd: %s", err);
+    auto kern = attention_tc2_kernel<T, D, STAGES>;
+    const int smem = L::TOTAL + 1024;
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) return fail(ENC_ERR_LAUNCH, "enc_attention_fwd: cannot opt in to %d bytes of shared memory: %s", smem, cudaGetErrorString(e));
+    dim3 grid((unsigned)cdiv(args.seq, 2 * BM), (unsigned)bh);
+    kern<<<grid, kThreads2, smem, st>>>(tq, tk, tv, args);
+    return check_launch("enc_attention_fwd");
+}
+
 template <typename T>
 int launch_attention(const void *q, const void *k, const void *v, AttnArgs args, int64_t bh, int64_t d, int variant,
                      cudaStream_t st) {
@@ -476,10 +808,13 @@ int launch_attention(const void *q, const void *k, const void *v, AttnArgs args,
     args.error = device_error_word();
     if (!args.error) return fail(ENC_ERR_NO_MEMORY, "enc_attention_fwd: cannot allocate the device status word");
     if constexpr (sizeof(T) == 2) {
+        if (variant < 0) variant = args.seq > BM ? 0 : 1;  // two tiles per CTA once there are two tiles
         if (d == 128) {
-            return variant == 1 ? launch_tc<T, 128, 3>(q, k, v, args, bh, st) : launch_tc<T, 128, 4>(q, k, v, args, bh, st);
+            if (variant == 0) return launch_tc2<T, 128, 3>(q, k, v, args, bh, st);
+            return variant == 2 ? launch_tc<T, 128, 3>(q, k, v, args, bh, st) : launch_tc<T, 128, 4>(q, k, v, args, bh, st);
         }
-        return variant == 1 ? launch_tc<T, 64, 3>(q, k, v, args, bh, st) : launch_tc<T, 64, 4>(q, k, v, args, bh, st);
+        if (variant == 0) return launch_tc2<T, 64, 6>(q, k, v, args, bh, st);
+        return variant == 2 ? launch_tc<T, 64, 3>(q, k, v, args, bh, st) : launch_tc<T, 64, 4>(q, k, v, args, bh, st);
     }
     return fail(ENC_ERR_UNSUPPORTED, "enc_attention_fwd: unreachable");
 }
@@ -488,7 +823,8 @@ int launch_attention(const void *q, const void *k, const void *v, AttnArgs args,
 
 int attention_variants() { return ATTN_VARIANTS; }
 void attention_variant_info(int v, char *out, size_t n) {
-    snprintf(out, n, "block_m=128 block_n=128 kv_stages=%d tcgen05 S/O in TMEM, P through shared memory", v == 1 ? 3 : 4);
+    if (v == 0) snprintf(out, n, "block_m=256 (two 128-row tiles, one softmax warpgroup each) block_n=128 tcgen05 S/O in TMEM, P through shared memory");
+    else snprintf(out, n, "block_m=128 block_n=128 kv_stages=%d tcgen05 S/O in TMEM, P through shared memory", v == 2 ? 3 : 4);
 }
 
 }  // namespace enc
