@@ -99,13 +99,13 @@ def workloads(scale: float = 1.0):
         return g
 
     # ---- config 1: softmax fp32 [4096, 1024] ----
-    def softmax_wl():
-        m, n = 4096, 1024
+    def softmax_wl(n=1024):
+        m = 4096
         return dict(
-            name="softmax_f32_4096x1024", kernel="softmax", jit=ops.softmax_kernel, unit="GB/s", bound="hbm", dtype="f32",
+            name=f"softmax_f32_4096x{n}", kernel="softmax", jit=ops.softmax_kernel, unit="GB/s", bound="hbm", dtype="f32",
             work=2 * m * n * 4, set_bytes=2 * m * n * 4,
             make=lambda i: (torch.randn(m, n, device="cuda", generator=gen(i)) * 4, torch.empty(m, n, device="cuda")),
-            run=lambda s: ops.softmax_kernel[(m,)](s[1], s[0], n, n, n, BLOCK=1024),
+            run=lambda s: ops.softmax_kernel[(m,)](s[1], s[0], n, n, n, BLOCK=n),
             host=lambda: (np.random.default_rng(0).standard_normal((m, n)).astype(np.float32) * 4,),
             run_host=lambda h: ops.softmax(h[0]),
             cpu=lambda h: O.softmax(h[0]), cpu_units=2 * m * n * 4)
@@ -245,6 +245,7 @@ def workloads(scale: float = 1.0):
                     cpu=lambda h: O.cumsum(h[0]), cpu_units=2 * nh * 4)
 
     W["softmax"] = softmax_wl
+    W["softmax_4096x4096"] = lambda: softmax_wl(4096)  # the reference's own benchmark shape (benchmarks/bench_softmax.py)
     W["layernorm"] = lambda: norm_wl("layernorm")
     W["rmsnorm"] = lambda: norm_wl("rmsnorm")
     W["gelu"] = gelu_wl

@@ -65,6 +65,7 @@ SIGNATURES: dict[str, list] = {
     "enc_matmul": [_p, _p, _p, _p, _i64, _i64, _i64, _i64, _i64, _i64, _i, _i, _i, _p],
     "enc_attention_fwd": [_p, _p, _p, _p, _p, _i64, _i64, _i64, _i64, _i64, _f, _i, _i, _i, _p],
     "enc_test_fail_next": [_i],
+    "enc_test_device_wait": [C.c_uint, _p],
 }
 _RESTYPES = {"enc_last_error": C.c_char_p, "enc_test_fail_next": None}
 

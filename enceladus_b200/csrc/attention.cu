@@ -54,41 +54,6 @@ struct AttnArgs {
 #define PROF_ADD(i) do {} while (0)
 #endif
 
-// ---- exponentials and P rounding off the special-function unit --------------------------------------
-// A 128 x 128 score block needs 16384 exponentials and 8192 two-value conversions; at 16 results per clock
-// per SM the special-function unit would be busy for longer than the two matrix products of the block.
-// Half of the exponentials are therefore evaluated on the FMA pipes, and bfloat16 rounding is done with
-// integer adds and a byte permute instead of a conversion instruction.
-
-// 2^x for x <= ~100 without the special-function unit: x = i + f with i integer and f in [-0.5, 0.5],
-// 2^f by a cubic (max relative error 7.7e-5, below the bfloat16/float16 rounding of P), the exponent field
-// adjusted by i.  Inputs below -126 (masked scores) give 2^-126 instead of zero.
-__device__ __forceinline__ float exp2_fma(float x) {
-    x = fmaxf(x, -126.0f);
-    const float t = x + 12582912.0f;  // 1.5 * 2^23: the sum rounds x to the nearest integer in the low mantissa bits
-    const float f = x - (t - 12582912.0f);
-    float p = fmaf(f, 0.05508868396282196f, 0.24260404706001282f);
-    p = fmaf(p, f, 0.6932762265205383f);
-    p = fmaf(p, f, 0.9999289512634277f);
-    return __uint_as_float(__float_as_uint(p) + (__float_as_uint(t) << 23));
-}
-
-// eight float32 bit patterns -> eight values of the input type in 16 bytes
-template <typename T> __device__ __forceinline__ uint4 pack_p(const uint32_t *v);
-template <> __device__ __forceinline__ uint4 pack_p<__half>(const uint32_t *v) {
-    float f[8];
-#pragma unroll
-    for (int i = 0; i < 8; ++i) f[i] = __uint_as_float(v[i]);
-    return Pack<__half>::pack(f);
-}
-template <> __device__ __forceinline__ uint4 pack_p<__nv_bfloat16>(const uint32_t *v) {
-    // round to nearest (ties away from zero; P is non-negative and finite): add half an ulp, keep the high halves
-    uint32_t w[4];
-#pragma unroll
-    for (int i = 0; i < 4; ++i) w[i] = __byte_perm(v[2 * i] + 0x8000u, v[2 * i + 1] + 0x8000u, 0x7632);
-    return make_uint4(w[0], w[1], w[2], w[3]);
-}
-
 // One row of one score block, in registers: mask, running maximum with lazy rescale, probabilities in
 // place (float32 bit patterns), row sum.  `alpha` is the factor the accumulator must be scaled by (1 when
 // no rescale is due).
@@ -119,13 +84,16 @@ __device__ __forceinline__ void softmax_row(uint32_t (&sv)[4][32], float qk_scal
         m_ref = m_new;
     }
     const float neg_m = m_ref == -INFINITY ? 0.0f : -m_ref;
-    float sum0 = 0.0f, sum1 = 0.0f;
+    // Evaluating part of the exponentials with a polynomial on the FMA pipes, and rounding P with integer
+    // operations, were both measured and both lost: a softmax warp is bound by its own instruction stream,
+    // not by the special-function unit, so extra instructions cost more than they free.
+    float sum0 = 0.0f, sum1 = 0.0f;  // two chains halve the dependent-add latency
 #pragma unroll
     for (int c = 0; c < 4; ++c)
 #pragma unroll
         for (int i = 0; i < 32; i += 2) {
-            const float p0 = fast_exp2(fmaf(__uint_as_float(sv[c][i]), qk_scale, neg_m));     // special-function unit
-            const float p1 = exp2_fma(fmaf(__uint_as_float(sv[c][i + 1]), qk_scale, neg_m));  // FMA pipes
+            const float p0 = fast_exp2(fmaf(__uint_as_float(sv[c][i]), qk_scale, neg_m));
+            const float p1 = fast_exp2(fmaf(__uint_as_float(sv[c][i + 1]), qk_scale, neg_m));
             sum0 += p0;
             sum1 += p1;
             sv[c][i] = __float_as_uint(p0);
@@ -143,7 +111,10 @@ template <typename T> __device__ __forceinline__ void store_p_row(uint8_t *p_row
 #pragma unroll
         for (int q4 = 0; q4 < 4; ++q4) {
             const int chunk = (c & 1) * 4 + q4;
-            *reinterpret_cast<uint4 *>(box + ((chunk ^ (r & 7)) << 4)) = pack_p<T>(&sv[c][q4 * 8]);
+            float pf[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) pf[i] = __uint_as_float(sv[c][q4 * 8 + i]);
+            *reinterpret_cast<uint4 *>(box + ((chunk ^ (r & 7)) << 4)) = Pack<T>::pack(pf);
         }
     }
 }
@@ -582,10 +553,12 @@ attention_tc2_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
         const int64_t tile_m0 = m0 + t * BM;
         float m_ref = -INFINITY, l = 0.0f;
         bool ok = true;
+        PROF_T0();
         for (int j = 0; j < my_nkv && ok; ++j) {
             ok = mbar_wait(&s_full[t], j & 1, abort);
             if (!ok) break;
             tc_fence_after();
+            if (warp == 4) PROF_ADD(0);
             const int64_t n0 = (int64_t)j * BN;
             const bool need_mask = (n0 + BN > a.seq) || (a.causal && n0 + BN > tile_m0);
             uint32_t sv[4][32];
@@ -594,12 +567,15 @@ attention_tc2_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
             tmem_ld_wait();
             tc_fence_before();
             mbar_arrive(&s_empty[t]);  // S_t(j) is in registers: the buffer can take S_t(j+1)
+            if (warp == 4) PROF_ADD(1);
             float alpha;
             bool rescale;
             softmax_row(sv, a.qk_scale, need_mask, n0, row, a.seq, a.causal, m_ref, l, alpha, rescale);
+            if (warp == 4) PROF_ADD(2);
             ok = mbar_wait(&p_empty[t], (j & 1) ^ 1, abort);  // P_t(j-1) V done: P buffer free, O_t quiescent
             if (!ok) break;
             tc_fence_after();
+            if (warp == 4) PROF_ADD(3);
             if (j > 0 && __any_sync(0xffffffffu, rescale)) {
 #pragma unroll 1
                 for (int c0 = 0; c0 < D; c0 += 32) {
@@ -616,6 +592,7 @@ attention_tc2_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
             store_p_row<T>(p_row, r, sv);
             fence_proxy_async();
             mbar_arrive(&p_full[t]);
+            if (warp == 4) PROF_ADD(4);
         }
         // ---- epilogue: O_t / l ----
         if (ok && my_nkv > 0) ok = mbar_wait(o_full, 0, abort);
@@ -787,8 +764,23 @@ int launch_tc2(const void *q, const void *k, const void *v, const AttnArgs &args
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return fail(ENC_ERR_LAUNCH, "enc_attention_fwd: cannot opt in to %d bytes of shared memory: %s", smem, cudaGetErrorString(e));
     dim3 grid((unsigned)cdiv(args.seq, 2 * BM), (unsigned)bh);
+#ifdef ENC_ATTN_PROF
+    AttnArgs pa = args;
+    cudaMallocManaged(&pa.prof, 16 * 8);
+    memset(pa.prof, 0, 16 * 8);
+    kern<<<grid, kThreads2, smem, st>>>(tq, tk, tv, pa);
+    cudaDeviceSynchronize();
+    {
+        const double blocks = (double)grid.x * grid.y * (double)cdiv(args.seq, BN) * (args.causal ? 0.5 : 1.0);
+        const char *names[5] = {"sm wait s_full", "sm load S", "sm max+exp", "sm wait p_empty", "sm rescale+store P"};
+        for (int i = 0; i < 5; ++i) printf("  prof2 %-20s %9.0f cycles per kv block (tile 0)\n", names[i], (double)pa.prof[i] / blocks);
+    }
+    cudaFree(pa.prof);
+    return check_launch("enc_attention_fwd");
+#else
     kern<<<grid, kThreads2, smem, st>>>(tq, tk, tv, args);
     return check_launch("enc_attention_fwd");
+#endif
 }
 
 template <typename T>

@@ -121,6 +121,30 @@ bool make_tensor_map(CUtensorMap *map, const void *base, int elem_is_bf16, int r
 
 }  // namespace enc
 
+namespace enc {
+namespace {
+// Polls a word that nothing ever sets, `polls` times at most, then gives up the way every bounded
+// device-side wait of the library does: it raises the device status word and returns.
+__global__ void wait_timeout_kernel(const unsigned int *never_set, unsigned int *error, unsigned int polls) {
+    unsigned int seen = 0;
+    for (unsigned int i = 0; i < polls && !seen; ++i) {
+        asm volatile("ld.relaxed.gpu.global.u32 %0, [%1];" : "=r"(seen) : "l"(never_set) : "memory");
+        __nanosleep(1000);
+    }
+    if (!seen) atomicExch(error, 6u);
+}
+}  // namespace
+}  // namespace enc
+
+extern "C" int enc_test_device_wait(unsigned int polls, void *stream) {
+    ENC_PROLOGUE();
+    if (polls > 1000000u) return enc::fail(ENC_ERR_BAD_ARG, "enc_test_device_wait: at most 1000000 polls (about one second)");
+    unsigned int *block = enc::device_error_word();
+    if (!block) return enc::fail(ENC_ERR_NO_MEMORY, "enc_test_device_wait: cannot allocate the device status word");
+    enc::wait_timeout_kernel<<<1, 1, 0, enc::as_stream(stream)>>>(block + 8, block, polls);  // word 8 of the block stays zero
+    return enc::check_launch("enc_test_device_wait");
+}
+
 extern "C" const char *enc_last_error(void) { return enc::g_error; }
 
 extern "C" void enc_test_fail_next(int status) { enc::g_forced = status; }

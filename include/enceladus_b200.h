@@ -203,6 +203,13 @@ int enc_attention_fwd(const void *q, const void *k, const void *v, void *o, floa
  * proxy around its native stream, tests/test_runtime.py:460-514).  0 clears it. */
 void enc_test_fail_next(int status);
 
+/* Launches one thread that polls a flag nothing sets, `polls` times at most (1 us apart, polls <=
+ * 1000000), then gives up exactly as the library's bounded device-side waits do: it raises the device
+ * status word and returns, so the next enc_synchronize reports ENC_ERR_DEVICE_WAIT and the context stays
+ * usable.  Exercises the timeout path without hanging or faulting the GPU (the reference tests its
+ * lost-sentinel timeout the same way, with a bounded wait: src/enceladus/runtime/stream.py:153-168). */
+int enc_test_device_wait(unsigned int polls, void *stream);
+
 #ifdef __cplusplus
 }
 #endif

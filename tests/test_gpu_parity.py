@@ -337,6 +337,23 @@ def test_injected_failure_surfaces_as_cuda_error():
     enceladus.synchronize()
 
 
+def test_bounded_device_wait_surfaces_at_synchronize_and_the_context_survives(oracle):
+    """A device-side wait that runs out (a flag nothing sets, 2000 polls of 1 us) must not hang: the kernel
+    returns, the next synchronize raises, and later launches work."""
+    import torch
+
+    stream = torch.cuda.current_stream().cuda_stream
+    N.call("enc_test_device_wait", 2000, stream)
+    with pytest.raises(enceladus.CudaError, match="device-side wait") as info:
+        enceladus.synchronize()
+    assert info.value.status == N.ERR_DEVICE_WAIT
+    enceladus.synchronize()  # the status word was cleared by the report
+    x = np.random.default_rng(13).standard_normal((4, 64)).astype(np.float32)
+    assert_close(host(ops.softmax(torch_of(x))), oracle.softmax(x))
+    with pytest.raises(ValueError, match="polls"):
+        N.call("enc_test_device_wait", 2_000_000, stream)
+
+
 def test_device_info_reports_blackwell():
     info = N.device_info()
     assert info.sm_count > 0 and info.cc_major >= 10, (info.cc_major, info.cc_minor)
