@@ -5,7 +5,7 @@
 // float32 accumulators in tensor memory:
 //     S = Q K^T    (128 x 128, A = Q K-major, B = K block K-major)      -> TMEM, double buffered
 //     O += P V     (128 x D,   A = P K-major in shared memory, B = V block MN-major) -> TMEM
-//   warp 0      TMA producer (Q once, then K0 V0 K1 V1 ... through the ring)
+//   warp 0      TMA producer (Q once, then K0, K1 V0, K2 V1, ... through the ring: the order of consumption)
 //   warp 1      MMA issuer; S of block j+1 is issued before P V of block j so that the tensor core
 //               works while the softmax warps are busy with block j
 //   warps 2..5  softmax: thread i owns query row i.  Base-2 online softmax in float32 on the scaled
@@ -48,7 +48,7 @@ struct AttnArgs {
 
 #ifdef ENC_ATTN_PROF
 #define PROF_T0() long long t_prof = clock64()
-#define PROF_ADD(i) do { long long t_now = clock64(); if (a.prof && lane == 0) atomicAdd(a.prof + (i), (unsigned long long)(t_now - t_prof)); t_prof = t_now; } while (0)
+#define PROF_ADD(i) do { long long t_now = clock64(); if (lane == 0) prof_acc[i] += t_now - t_prof; t_prof = t_now; } while (0)
 #else
 #define PROF_T0() do {} while (0)
 #define PROF_ADD(i) do {} while (0)
@@ -191,13 +191,17 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
             for (int b = 0; b < D / 64; ++b) tma_load_3d(smem + L::Q_OFF + b * (BM * 128), &tm_q, q_full, b * 64, (int)m0, bh);
             bool ok = true;
             uint32_t stage = 0, phase = 0;
-            for (int it = 0; it < 2 * nkv && ok; ++it) {  // K0 V0 K1 V1 ...
-                const int j = it >> 1;
+            // Blocks are fetched in the order the MMA warp consumes them - K0, K1 V0, K2 V1, ... , V(n-1) - so
+            // that the slot a V block frees at the end of one step refills with the K block of the step after next
+            // while a whole step is still ahead of it.
+            for (int it = 0; it < 2 * nkv && ok; ++it) {
+                const bool is_v = it == 2 * nkv - 1 || (it != 0 && (it & 1) == 0);
+                const int j = it == 0 ? 0 : it == 2 * nkv - 1 ? nkv - 1 : is_v ? (it - 2) >> 1 : (it + 1) >> 1;
                 ok = mbar_wait(&kv_empty[stage], phase ^ 1, abort);
                 if (!ok) break;
                 uint8_t *dst = smem + L::KV_OFF + stage * L::TILE;
                 mbar_expect_tx(&kv_full[stage], L::TILE);
-                const CUtensorMap *tm = (it & 1) ? &tm_v : &tm_k;
+                const CUtensorMap *tm = is_v ? &tm_v : &tm_k;
 #pragma unroll
                 for (int b = 0; b < D / 64; ++b) tma_load_3d(dst + b * (BN * 128), tm, &kv_full[stage], b * 64, j * BN, bh);
                 if (++stage == STAGES) { stage = 0; phase ^= 1; }
@@ -217,11 +221,13 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
             const uint32_t idesc_o = idesc_f16(a.is_bf16, /*b_mn_major=*/true, BM, D);
             const uint32_t sq = smem_u32(smem + L::Q_OFF), sp = smem_u32(smem + L::P_OFF);
             bool ok = mbar_wait(q_full, 0, abort);
-            // ring position of tile `it` (K_j = 2j, V_j = 2j+1)
+            // ring positions in the producer's order: K_j is item 2j-1 (K_0 item 0), V_j item 2j+2 (the last V item 2n-1)
             auto slot = [&](int it, uint32_t &stage, uint32_t &phase) { stage = it % STAGES; phase = (it / STAGES) & 1; };
+            auto k_item = [&](int j) { return j == 0 ? 0 : 2 * j - 1; };
+            auto v_item = [&](int j) { return 2 * j + 2 < 2 * nkv - 1 ? 2 * j + 2 : 2 * nkv - 1; };
             auto issue_s = [&](int j) -> bool {  // S_j = Q K_j^T into S buffer j & 1
                 uint32_t stage, phase;
-                slot(2 * j, stage, phase);
+                slot(k_item(j), stage, phase);
                 if (!mbar_wait(&kv_full[stage], phase, abort)) return false;
                 if (!mbar_wait(&s_empty[j & 1], ((j >> 1) & 1) ^ 1, abort)) return false;
                 tc_fence_after();
@@ -237,19 +243,15 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
                 return true;
             };
             if (ok && nkv > 0) ok = issue_s(0);
-            PROF_T0();
             for (int j = 0; j < nkv && ok; ++j) {
                 if (j + 1 < nkv) {
                     ok = issue_s(j + 1);
                     if (!ok) break;
                 }
-                PROF_ADD(8);
                 uint32_t stage, phase;
-                slot(2 * j + 1, stage, phase);
+                slot(v_item(j), stage, phase);
                 ok = mbar_wait(&kv_full[stage], phase, abort);
-                PROF_ADD(9);
                 ok = ok && mbar_wait(p_full, j & 1, abort);
-                PROF_ADD(10);
                 if (!ok) break;
                 tc_fence_after();
                 const uint32_t sv = smem_u32(smem + L::KV_OFF + stage * L::TILE);
@@ -262,7 +264,6 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
                 }
                 tc_commit(&kv_empty[stage]);
                 tc_commit(p_empty);
-                PROF_ADD(11);
             }
             if (ok) tc_commit(o_full);
         }
@@ -275,12 +276,10 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
         uint8_t *p_row = smem + L::P_OFF + r * 128;
         float m_ref = -INFINITY, l = 0.0f;
         bool ok = true;
-        PROF_T0();
         for (int j = 0; j < nkv && ok; ++j) {
             ok = mbar_wait(&s_full[j & 1], (j >> 1) & 1, abort);
             if (!ok) break;
             tc_fence_after();
-            if (warp == 2) PROF_ADD(0);
             const uint32_t t_s = tmem_base + lane_addr + S_COL + (j & 1) * BN;
             const int64_t n0 = (int64_t)j * BN;
             const bool need_mask = (n0 + BN > a.seq) || (a.causal && n0 + BN > m0);
@@ -292,16 +291,13 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
             tmem_ld_wait();
             tc_fence_before();
             mbar_arrive(&s_empty[j & 1]);  // S(j) is in registers: the buffer can take S(j+2)
-            if (warp == 2) PROF_ADD(1);
             float alpha;
             bool rescale;
             softmax_row(sv, a.qk_scale, need_mask, n0, row, a.seq, a.causal, m_ref, l, alpha, rescale);
-            if (warp == 2) PROF_ADD(2);
             // P(j-1) V has finished: the P buffer is free and O is quiescent
             ok = mbar_wait(p_empty, (j & 1) ^ 1, abort);
             if (!ok) break;
             tc_fence_after();
-            if (warp == 2) PROF_ADD(3);
             if (j > 0 && __any_sync(0xffffffffu, rescale)) {
 #pragma unroll 1
                 for (int c0 = 0; c0 < D; c0 += 32) {
@@ -318,7 +314,6 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
             store_p_row<T>(p_row, r, sv);
             fence_proxy_async();  // make the P stores visible to the tensor core
             mbar_arrive(p_full);
-            if (warp == 2) PROF_ADD(4);
         }
         // ---- epilogue: O / l ----
         if (ok && nkv > 0) ok = mbar_wait(o_full, 0, abort);
@@ -356,53 +351,69 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
     }
 }
 
-// ---- two query tiles per CTA -------------------------------------------------------------------------
+// ---- two query tiles per CTA, P in tensor memory --------------------------------------------------------
 // The softmax of one 128-row tile takes longer than its two matrix products, so with a single tile per
-// CTA the tensor core idles about half of the time.  This kernel gives every CTA 256 query rows as two
-// independent 128-row tiles, each with its own softmax warpgroup, accumulator and score buffer in
-// tensor memory: while one warpgroup exponentiates, the tensor core serves the other tile, and every
-// K/V block fetched into shared memory is used twice.
+// CTA the tensor core idles most of the time.  This kernel gives every CTA 256 query rows as two
+// independent 128-row tiles, each with its own softmax warpgroup, accumulator and score buffer in tensor
+// memory: while one warpgroup exponentiates, the tensor core serves the other tile, and every K/V block
+// fetched into shared memory is used twice.
 //   warpgroup 0   warp 0 = TMA producer, warp 1 = MMA issuer (registers released with setmaxnreg)
 //   warpgroup 1   softmax of tile 0          warpgroup 2   softmax of tile 1
-// TMEM columns: S0 [0,128) S1 [128,256) O0 [256,256+D) O1 [384,384+D).  Issue order per K/V block j:
-// S0(j+1), P0(j)V, S1(j+1), P1(j)V - each score product goes out as soon as the tile's softmax has pulled
-// the previous scores into registers.
+// With P staged through shared memory every step moves, per pair of tiles, 256 KB of MMA operands, 64 KB of
+// P stores and 64 KB of TMA writes through the shared-memory port: about 3000 cycles at 128 bytes per cycle,
+// more than the 2048 cycles of tensor-core work.  Here the softmax threads write P (rounded to the input
+// type, two values per 32-bit column) straight back into tensor memory, over the first 64 columns of the
+// score block they have just pulled into registers, and P V reads its A operand from there: no P traffic in
+// shared memory, no proxy fence, and the room P took goes to a deeper K/V ring.
+//   TMEM columns: S0/P0 [0,128)  S1/P1 [128,256)  O0 [256,256+D)  O1 [384,384+D)
+//   issue order per K/V block j: P0(j)V, S0(j+1), P1(j)V, S1(j+1).  S_t(j+1) overwrites P_t(j), so it follows
+//   P_t(j)V in the (in-order) MMA pipe; its completion also tells the softmax warpgroup that O_t is
+//   quiescent, so the softmax side waits on one barrier per step.
 constexpr int kThreads2 = 384;
 
-template <int D, int STAGES> struct AttnSmem2 {
+template <int D, int STAGES> struct AttnSmemTs {
     static constexpr int TILE = BM * D * 2;
-    static constexpr int Q_OFF = 0;                       // 2 query tiles
-    static constexpr int P_OFF = 2 * TILE;                // 2 probability tiles of 128 x 128
-    static constexpr int P_BYTES = BM * BN * 2;
-    static constexpr int KV_OFF = P_OFF + 2 * P_BYTES;
+    static constexpr int Q_OFF = 0;  // 2 query tiles
+    static constexpr int KV_OFF = 2 * TILE;
     static constexpr int BAR_OFF = KV_OFF + STAGES * TILE;
-    static constexpr int NBARS = 1 + 2 * STAGES + 8 + 1;  // q, kv full/empty, (s_full, s_empty, p_full, p_empty) x 2, o
+    static constexpr int NBARS = 1 + 2 * STAGES + 4 + 1;  // q, kv full/empty, (s_full, p_full) x 2, o
     static constexpr int TOTAL = BAR_OFF + NBARS * 8 + 16;
 };
 
+template <typename T> __device__ __forceinline__ uint32_t pack_pair(float lo, float hi);
+template <> __device__ __forceinline__ uint32_t pack_pair<__half>(float lo, float hi) {
+    const __half2 h = __floats2half2_rn(lo, hi);
+    return *reinterpret_cast<const uint32_t *>(&h);
+}
+template <> __device__ __forceinline__ uint32_t pack_pair<__nv_bfloat16>(float lo, float hi) {
+    const __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<const uint32_t *>(&h);
+}
+
 template <typename T, int D, int STAGES>
 __global__ void __launch_bounds__(kThreads2, 1)
-attention_tc2_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
-                     const __grid_constant__ CUtensorMap tm_v, AttnArgs a) {
-    using L = AttnSmem2<D, STAGES>;
+attention_ts_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
+                    const __grid_constant__ CUtensorMap tm_v, AttnArgs a) {
+    using L = AttnSmemTs<D, STAGES>;
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint64_t *q_full = reinterpret_cast<uint64_t *>(smem + L::BAR_OFF);
     uint64_t *kv_full = q_full + 1;
     uint64_t *kv_empty = kv_full + STAGES;
     uint64_t *s_full = kv_empty + STAGES;  // [2] one per tile
-    uint64_t *s_empty = s_full + 2;
-    uint64_t *p_full = s_empty + 2;
-    uint64_t *p_empty = p_full + 2;
-    uint64_t *o_full = p_empty + 2;
+    uint64_t *p_full = s_full + 2;         // [2]
+    uint64_t *o_full = p_full + 2;
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(o_full + 1);
     volatile uint32_t *abort = tmem_slot + 1;
 
+#ifdef ENC_ATTN_PROF
+    __shared__ long long prof_acc[16];
+    if (threadIdx.x < 16) prof_acc[threadIdx.x] = 0;
+#endif
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int qb = a.causal ? (int)(gridDim.x - 1 - blockIdx.x) : (int)blockIdx.x;  // heavy blocks first
     const int bh = blockIdx.y;
     const int64_t m0 = (int64_t)qb * (2 * BM);
-    // key blocks each tile needs: all of them, or up to its own diagonal; none for a tile past the sequence
     int nkv_t[2];
 #pragma unroll
     for (int t = 0; t < 2; ++t) {
@@ -421,9 +432,7 @@ attention_tc2_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
         }
         for (int t = 0; t < 2; ++t) {
             mbar_init(&s_full[t], 1);
-            mbar_init(&s_empty[t], 128);
             mbar_init(&p_full[t], 128);
-            mbar_init(&p_empty[t], 1);
         }
         mbar_init(o_full, 1);
         *abort = 0;
@@ -441,7 +450,7 @@ attention_tc2_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
     if (warp < 4) {
         asm volatile("setmaxnreg.dec.sync.aligned.u32 56;");
         if (warp == 0 && lane == 0) {
-            // ---------------- TMA producer ----------------
+            // ---------------- TMA producer: Q tiles, then K0 V0 K1 V1 ... (the order of consumption) ----------------
             mbar_expect_tx(q_full, 2 * L::TILE);
 #pragma unroll
             for (int t = 0; t < 2; ++t)
@@ -450,7 +459,7 @@ attention_tc2_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
                     tma_load_3d(smem + L::Q_OFF + t * L::TILE + b * (BM * 128), &tm_q, q_full, b * 64, (int)(m0 + t * BM), bh);
             bool ok = true;
             uint32_t stage = 0, phase = 0;
-            for (int it = 0; it < 2 * nkv && ok; ++it) {  // K0 V0 K1 V1 ...
+            for (int it = 0; it < 2 * nkv && ok; ++it) {
                 const int j = it >> 1;
                 ok = mbar_wait(&kv_empty[stage], phase ^ 1, abort);
                 if (!ok) break;
@@ -474,67 +483,78 @@ attention_tc2_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
             const uint32_t idesc_o = idesc_f16(a.is_bf16, /*b_mn_major=*/true, BM, D);
             bool ok = mbar_wait(q_full, 0, abort);
             auto slot = [&](int it, uint32_t &stage, uint32_t &phase) { stage = it % STAGES; phase = (it / STAGES) & 1; };
-            auto mma_s = [&](int t, int j, uint32_t sk) -> bool {  // S_t = Q_t K_j^T
-                if (!mbar_wait(&s_empty[t], (j & 1) ^ 1, abort)) return false;
-                tc_fence_after();
-                const uint32_t sq = smem_u32(smem + L::Q_OFF + t * L::TILE);
+            // descriptor halves: the high half is one constant, the low halves are a base plus a constant per step
+            constexpr uint32_t desc_hi = smem_desc_hi_sw128(1024);
+            const uint32_t q_lo = smem_desc_lo(smem_u32(smem + L::Q_OFF), 16);
+            const uint32_t k_lo = smem_desc_lo(smem_u32(smem + L::KV_OFF), 16);
+            const uint32_t v_lo = smem_desc_lo(smem_u32(smem + L::KV_OFF), BN * 128);
+            auto mma_s = [&](int t, uint32_t stage) {  // S_t = Q_t K^T
+                const uint32_t qa = q_lo + t * (L::TILE >> 4), kb = k_lo + stage * (L::TILE >> 4);
 #pragma unroll
                 for (int kk = 0; kk < D / 16; ++kk) {
-                    const uint32_t off = (kk >> 2) * (BM * 128) + (kk & 3) * 32;
-                    tc_mma_f16(tmem_base + t * BN, smem_desc_sw128(sq + off, 16, 1024), smem_desc_sw128(sk + off, 16, 1024), idesc_s, kk != 0);
+                    const uint32_t off = ((kk >> 2) * (BM * 128) + (kk & 3) * 32) >> 4;  // 64-wide box, then 32 bytes per step
+                    tc_mma_f16_halves(tmem_base + t * BN, qa + off, desc_hi, kb + off, desc_hi, idesc_s, kk != 0);
                 }
                 tc_commit(&s_full[t]);
-                return true;
             };
-            auto mma_pv = [&](int t, int j, uint32_t sv) -> bool {  // O_t += P_t V_j
+#ifdef ENC_ATTN_PROF
+            long long t_prof = 0;
+#endif
+            auto mma_pv = [&](int t, int j, uint32_t stage) -> bool {  // O_t += P_t V_j, P_t from tensor memory
                 if (!mbar_wait(&p_full[t], j & 1, abort)) return false;
                 tc_fence_after();
-                const uint32_t sp = smem_u32(smem + L::P_OFF + t * L::P_BYTES);
+                PROF_ADD(9 + 2 * t);
+                const uint32_t vb = v_lo + stage * (L::TILE >> 4);
 #pragma unroll
-                for (int kk = 0; kk < BN / 16; ++kk) {
-                    const uint32_t poff = (kk >> 2) * (BM * 128) + (kk & 3) * 32;
-                    tc_mma_f16(tmem_base + 256 + t * 128, smem_desc_sw128(sp + poff, 16, 1024),
-                               smem_desc_sw128(sv + kk * 2048, BN * 128, 1024), idesc_o, (j | kk) != 0);
-                }
-                tc_commit(&p_empty[t]);
+                for (int kk = 0; kk < BN / 16; ++kk)  // 16 keys = 8 packed columns of P, 16 rows = 2048 bytes of V
+                    tc_mma_f16_ts_halves(tmem_base + 256 + t * 128, tmem_base + t * BN + kk * 8, vb + kk * (2048 >> 4), desc_hi,
+                                         idesc_o, (j | kk) != 0);
                 return true;
             };
             uint32_t stage, phase;
             if (ok && nkv > 0) {
                 slot(0, stage, phase);
                 ok = mbar_wait(&kv_full[stage], phase, abort);
-                const uint32_t sk = smem_u32(smem + L::KV_OFF + stage * L::TILE);
-                for (int t = 0; t < 2 && ok; ++t)
-                    if (nkv_t[t] > 0) ok = mma_s(t, 0, sk);
-                if (ok) tc_commit(&kv_empty[stage]);
-            }
-            for (int j = 0; j < nkv && ok; ++j) {
-                uint32_t kstage = 0, vstage;
-                uint32_t sk = 0;
-                const bool more = j + 1 < nkv;
-                if (more) {
-                    slot(2 * (j + 1), kstage, phase);
-                    ok = mbar_wait(&kv_full[kstage], phase, abort);
-                    if (!ok) break;
-                    sk = smem_u32(smem + L::KV_OFF + kstage * L::TILE);
+                if (ok) {
+                    tc_fence_after();
+#pragma unroll
+                    for (int t = 0; t < 2; ++t)
+                        if (nkv_t[t] > 0) mma_s(t, stage);
+                    tc_commit(&kv_empty[stage]);
                 }
+            }
+#ifdef ENC_ATTN_PROF
+            t_prof = clock64();
+#endif
+            for (int j = 0; j < nkv && ok; ++j) {
+                uint32_t vstage, kstage = 0;
                 slot(2 * j + 1, vstage, phase);
-                const uint32_t vphase = phase;
-                const uint32_t sv = smem_u32(smem + L::KV_OFF + vstage * L::TILE);
-                bool v_ready = false;
-                for (int t = 0; t < 2 && ok; ++t) {
-                    if (more && j + 1 < nkv_t[t]) ok = mma_s(t, j + 1, sk);
-                    if (ok && j < nkv_t[t]) {
-                        if (!v_ready) {
-                            ok = mbar_wait(&kv_full[vstage], vphase, abort);
-                            v_ready = true;
+                ok = mbar_wait(&kv_full[vstage], phase, abort);
+                if (!ok) break;
+                PROF_ADD(8);
+                const bool more = j + 1 < nkv;  // then at least one tile takes K(j+1)
+                bool k_ready = false;
+#pragma unroll
+                for (int t = 0; t < 2; ++t) {
+                    if (!ok) break;
+                    if (j < nkv_t[t]) ok = mma_pv(t, j, vstage);
+                    if (t == 1 && ok) tc_commit(&kv_empty[vstage]);  // V(j) is free once both products have run
+                    if (ok && j + 1 < nkv_t[t]) {
+                        if (!k_ready) {
+                            PROF_ADD(14);
+                            slot(2 * j + 2, kstage, phase);
+                            ok = mbar_wait(&kv_full[kstage], phase, abort);
+                            if (!ok) break;
+                            tc_fence_after();
+                            PROF_ADD(13);
+                            k_ready = true;
                         }
-                        if (ok) ok = mma_pv(t, j, sv);
+                        mma_s(t, kstage);
                     }
+                    PROF_ADD(10 + 2 * t);
                 }
                 if (!ok) break;
                 if (more) tc_commit(&kv_empty[kstage]);
-                tc_commit(&kv_empty[vstage]);
             }
             if (ok) tc_commit(o_full);
         }
@@ -548,13 +568,13 @@ attention_tc2_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
         const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
         const uint32_t t_s = tmem_base + lane_addr + t * BN;
         const uint32_t t_o = tmem_base + lane_addr + 256 + t * 128;
-        uint8_t *p_row = smem + L::P_OFF + t * L::P_BYTES + r * 128;
         const int my_nkv = nkv_t[t];
         const int64_t tile_m0 = m0 + t * BM;
         float m_ref = -INFINITY, l = 0.0f;
         bool ok = true;
         PROF_T0();
         for (int j = 0; j < my_nkv && ok; ++j) {
+            // S_t(j) complete; the MMA pipe runs in order, so P_t(j-1) V is complete too and O_t is quiescent
             ok = mbar_wait(&s_full[t], j & 1, abort);
             if (!ok) break;
             tc_fence_after();
@@ -565,17 +585,11 @@ attention_tc2_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
 #pragma unroll
             for (int c = 0; c < 4; ++c) tmem_ld_32x32(t_s + c * 32, sv[c]);
             tmem_ld_wait();
-            tc_fence_before();
-            mbar_arrive(&s_empty[t]);  // S_t(j) is in registers: the buffer can take S_t(j+1)
             if (warp == 4) PROF_ADD(1);
             float alpha;
             bool rescale;
             softmax_row(sv, a.qk_scale, need_mask, n0, row, a.seq, a.causal, m_ref, l, alpha, rescale);
             if (warp == 4) PROF_ADD(2);
-            ok = mbar_wait(&p_empty[t], (j & 1) ^ 1, abort);  // P_t(j-1) V done: P buffer free, O_t quiescent
-            if (!ok) break;
-            tc_fence_after();
-            if (warp == 4) PROF_ADD(3);
             if (j > 0 && __any_sync(0xffffffffu, rescale)) {
 #pragma unroll 1
                 for (int c0 = 0; c0 < D; c0 += 32) {
@@ -586,11 +600,20 @@ attention_tc2_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
                     for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * alpha);
                     tmem_st_32x32(t_o + c0, v);
                 }
-                tmem_st_wait();
-                tc_fence_before();
             }
-            store_p_row<T>(p_row, r, sv);
-            fence_proxy_async();
+            // P_t(j), two values per column, over the first 64 columns of the score block
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                uint32_t pk[32];
+#pragma unroll
+                for (int i = 0; i < 32; ++i) {
+                    const int e = 2 * i;  // element inside this half of 64
+                    pk[i] = pack_pair<T>(__uint_as_float(sv[2 * h + (e >> 5)][e & 31]), __uint_as_float(sv[2 * h + (e >> 5)][(e & 31) + 1]));
+                }
+                tmem_st_32x32(t_s + h * 32, pk);
+            }
+            tmem_st_wait();
+            tc_fence_before();
             mbar_arrive(&p_full[t]);
             if (warp == 4) PROF_ADD(4);
         }
@@ -618,6 +641,9 @@ attention_tc2_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
 
     tc_fence_before();
     __syncthreads();
+#ifdef ENC_ATTN_PROF
+    if (threadIdx.x < 16 && a.prof) atomicAdd(a.prof + threadIdx.x, (unsigned long long)prof_acc[threadIdx.x]);
+#endif
     if (threadIdx.x == 0 && *abort) atomicExch(a.error, 4u);
     if (warp == 1) {
         tc_fence_after();
@@ -707,11 +733,11 @@ __global__ void __launch_bounds__(128) attention_simple_kernel(const T *q, const
     }
 }
 
-constexpr int ATTN_VARIANTS = 3;  // 0: two 128-row query tiles per CTA; 1, 2: one tile, 4- or 3-deep K/V ring
+constexpr int ATTN_VARIANTS = 3;  // 0: two 128-row query tiles per CTA, P in TMEM; 1, 2: one tile, P through shared memory, 4- or 3-deep K/V ring
 
-template <typename T, int D, int STAGES>
+// Tensor maps over [bh, seq, D] with 64 x 128 boxes, then the launch.  TILES = query tiles of 128 rows per CTA.
+template <typename T, int D, int STAGES, int TILES>
 int launch_tc(const void *q, const void *k, const void *v, const AttnArgs &args, int64_t bh, cudaStream_t st) {
-    using L = AttnSmem<D, STAGES>;
     char err[256];
     CUtensorMap tq, tk, tv;
     const uint64_t dims[3] = {(uint64_t)D, (uint64_t)args.seq, (uint64_t)bh};
@@ -721,66 +747,30 @@ int launch_tc(const void *q, const void *k, const void *v, const AttnArgs &args,
         !make_tensor_map(&tk, k, args.is_bf16, 3, dims, strides, box, err, sizeof(err)) ||
         !make_tensor_map(&tv, v, args.is_bf16, 3, dims, strides, box, err, sizeof(err)))
         return fail(ENC_ERR_LAUNCH, "enc_attention_fwd: %s", err);
-    auto kern = attention_tc_kernel<T, D, STAGES>;
-    const int smem = L::TOTAL + 1024;
+    auto kern = TILES == 2 ? attention_ts_kernel<T, D, STAGES> : attention_tc_kernel<T, D, STAGES>;
+    const int smem = (TILES == 2 ? AttnSmemTs<D, STAGES>::TOTAL : AttnSmem<D, STAGES>::TOTAL) + 1024;
+    const int threads = TILES == 2 ? kThreads2 : kThreads;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return fail(ENC_ERR_LAUNCH, "enc_attention_fwd: cannot opt in to %d bytes of shared memory: %s", smem, cudaGetErrorString(e));
-    dim3 grid((unsigned)cdiv(args.seq, BM), (unsigned)bh);
+    dim3 grid((unsigned)cdiv(args.seq, TILES * BM), (unsigned)bh);
 #ifdef ENC_ATTN_PROF
     AttnArgs pa = args;
     cudaMallocManaged(&pa.prof, 16 * 8);
     memset(pa.prof, 0, 16 * 8);
-    kern<<<grid, kThreads, smem, st>>>(tq, tk, tv, pa);
+    kern<<<grid, threads, smem, st>>>(tq, tk, tv, pa);
     cudaDeviceSynchronize();
     {
         const double blocks = (double)grid.x * grid.y * (double)cdiv(args.seq, BN) * (args.causal ? 0.5 : 1.0);
-        const char *names[12] = {"sm wait s_full", "sm load S", "sm max+exp", "sm wait p_empty", "sm rescale+store P", "", "", "",
-                                 "mma issue_s(j+1)", "mma wait V", "mma wait p_full", "mma issue PV"};
-        for (int i = 0; i < 12; ++i)
-            if (names[i][0]) printf("  prof %-20s %9.0f cycles per kv block\n", names[i], (double)pa.prof[i] / blocks);
+        const char *names[15] = {"sm wait s_full", "sm load S", "sm max+exp", "", "sm rescale+store P", "", "", "",
+                                 "mma wait V", "mma wait p_full0", "mma issue S0", "mma wait p_full1", "mma issue PV1 S1", "mma wait K", "mma issue PV0"};
+        for (int i = 0; i < 15; ++i)
+            if (pa.prof[i]) printf("  prof %-20s %9.0f cycles per kv block (tile 0)\n", names[i], (double)pa.prof[i] / blocks);
     }
     cudaFree(pa.prof);
-    return check_launch("enc_attention_fwd");
 #else
-    kern<<<grid, kThreads, smem, st>>>(tq, tk, tv, args);
-    return check_launch("enc_attention_fwd");
+    kern<<<grid, threads, smem, st>>>(tq, tk, tv, args);
 #endif
-}
-
-template <typename T, int D, int STAGES>
-int launch_tc2(const void *q, const void *k, const void *v, const AttnArgs &args, int64_t bh, cudaStream_t st) {
-    using L = AttnSmem2<D, STAGES>;
-    char err[256];
-    CUtensorMap tq, tk, tv;
-    const uint64_t dims[3] = {(uint64_t)D, (uint64_t)args.seq, (uint64_t)bh};
-    const uint64_t strides[2] = {(uint64_t)args.stride_m * 2, (uint64_t)args.stride_h * 2};
-    const uint32_t box[3] = {64, BM, 1};
-    if (!make_tensor_map(&tq, q, args.is_bf16, 3, dims, strides, box, err, sizeof(err)) ||
-        !make_tensor_map(&tk, k, args.is_bf16, 3, dims, strides, box, err, sizeof(err)) ||
-        !make_tensor_map(&tv, v, args.is_bf16, 3, dims, strides, box, err, sizeof(err)))
-        return fail(ENC_ERR_LAUNCH, "enc_attention_fwd: %s", err);
-    auto kern = attention_tc2_kernel<T, D, STAGES>;
-    const int smem = L::TOTAL + 1024;
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-    if (e != cudaSuccess) return fail(ENC_ERR_LAUNCH, "enc_attention_fwd: cannot opt in to %d bytes of shared memory: %s", smem, cudaGetErrorString(e));
-    dim3 grid((unsigned)cdiv(args.seq, 2 * BM), (unsigned)bh);
-#ifdef ENC_ATTN_PROF
-    AttnArgs pa = args;
-    cudaMallocManaged(&pa.prof, 16 * 8);
-    memset(pa.prof, 0, 16 * 8);
-    kern<<<grid, kThreads2, smem, st>>>(tq, tk, tv, pa);
-    cudaDeviceSynchronize();
-    {
-        const double blocks = (double)grid.x * grid.y * (double)cdiv(args.seq, BN) * (args.causal ? 0.5 : 1.0);
-        const char *names[5] = {"sm wait s_full", "sm load S", "sm max+exp", "sm wait p_empty", "sm rescale+store P"};
-        for (int i = 0; i < 5; ++i) printf("  prof2 %-20s %9.0f cycles per kv block (tile 0)\n", names[i], (double)pa.prof[i] / blocks);
-    }
-    cudaFree(pa.prof);
     return check_launch("enc_attention_fwd");
-#else
-    kern<<<grid, kThreads2, smem, st>>>(tq, tk, tv, args);
-    return check_launch("enc_attention_fwd");
-#endif
 }
 
 template <typename T>
@@ -802,11 +792,11 @@ int launch_attention(const void *q, const void *k, const void *v, AttnArgs args,
     if constexpr (sizeof(T) == 2) {
         if (variant < 0) variant = args.seq > BM ? 0 : 1;  // two tiles per CTA once there are two tiles
         if (d == 128) {
-            if (variant == 0) return launch_tc2<T, 128, 3>(q, k, v, args, bh, st);
-            return variant == 2 ? launch_tc<T, 128, 3>(q, k, v, args, bh, st) : launch_tc<T, 128, 4>(q, k, v, args, bh, st);
+            if (variant == 0) return launch_tc<T, 128, 5, 2>(q, k, v, args, bh, st);
+            return variant == 2 ? launch_tc<T, 128, 3, 1>(q, k, v, args, bh, st) : launch_tc<T, 128, 4, 1>(q, k, v, args, bh, st);
         }
-        if (variant == 0) return launch_tc2<T, 64, 6>(q, k, v, args, bh, st);
-        return variant == 2 ? launch_tc<T, 64, 3>(q, k, v, args, bh, st) : launch_tc<T, 64, 4>(q, k, v, args, bh, st);
+        if (variant == 0) return launch_tc<T, 64, 8, 2>(q, k, v, args, bh, st);
+        return variant == 2 ? launch_tc<T, 64, 3, 1>(q, k, v, args, bh, st) : launch_tc<T, 64, 4, 1>(q, k, v, args, bh, st);
     }
     return fail(ENC_ERR_UNSUPPORTED, "enc_attention_fwd: unreachable");
 }
@@ -815,7 +805,7 @@ int launch_attention(const void *q, const void *k, const void *v, AttnArgs args,
 
 int attention_variants() { return ATTN_VARIANTS; }
 void attention_variant_info(int v, char *out, size_t n) {
-    if (v == 0) snprintf(out, n, "block_m=256 (two 128-row tiles, one softmax warpgroup each) block_n=128 tcgen05 S/O in TMEM, P through shared memory");
+    if (v == 0) snprintf(out, n, "block_m=256 (two 128-row tiles, one softmax warpgroup each) block_n=128 tcgen05 S/P/O in TMEM");
     else snprintf(out, n, "block_m=128 block_n=128 kv_stages=%d tcgen05 S/O in TMEM, P through shared memory", v == 2 ? 3 : 4);
 }
 

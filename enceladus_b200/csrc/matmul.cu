@@ -138,6 +138,9 @@ matmul_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
         // ---------------- MMA issuer ----------------
         if (lane == 0) {
             const uint32_t idesc = idesc_f16(a.is_bf16, /*b_mn_major=*/true, BM, BN);
+            constexpr uint32_t desc_hi = smem_desc_hi_sw128(1024);
+            const uint32_t a_lo0 = smem_desc_lo(smem_u32(smem), 16);
+            const uint32_t b_lo0 = smem_desc_lo(smem_u32(smem + L::A_BYTES), BK * 128);
             uint32_t stage = 0, phase = 0, acc = 0, acc_phase = 0;
             bool ok = true;
             for (int64_t tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x) {
@@ -149,16 +152,13 @@ matmul_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
                     ok = mbar_wait(&full[stage], phase, abort);
                     if (!ok) break;
                     tc_fence_after();
-                    const uint32_t sa = smem_u32(smem + stage * L::STAGE_BYTES);
-                    const uint32_t sb = sa + L::A_BYTES;
+                    // Descriptor low halves: a base per stage plus a constant per step (A: 16 K-values = 32 bytes
+                    // further along the swizzled 128-byte rows; B: 16 K-rows = 2048 bytes further, 64-wide N blocks
+                    // BK*128 bytes apart).  The issuing thread does as little as possible per MMA.
+                    const uint32_t a_lo = a_lo0 + stage * (L::STAGE_BYTES >> 4), b_lo = b_lo0 + stage * (L::STAGE_BYTES >> 4);
 #pragma unroll
-                    for (int kk = 0; kk < BK / 16; ++kk) {
-                        // A: 16 K-values = 32 bytes further along the swizzled 128-byte rows.
-                        // B: 16 K-rows = 2048 bytes further; 64-wide N blocks are BK*128 bytes apart.
-                        const uint64_t da = smem_desc_sw128(sa + kk * 32, 16, 1024);
-                        const uint64_t db = smem_desc_sw128(sb + kk * 2048, BK * 128, 1024);
-                        tc_mma_f16(d_tmem, da, db, idesc, (k | kk) != 0);
-                    }
+                    for (int kk = 0; kk < BK / 16; ++kk)
+                        tc_mma_f16_halves(d_tmem, a_lo + kk * (32 >> 4), desc_hi, b_lo + kk * (2048 >> 4), desc_hi, idesc, (k | kk) != 0);
                     tc_commit(&empty[stage]);  // stage reusable once these MMAs have read it
                     if (++stage == STAGES) { stage = 0; phase ^= 1; }
                 }
