@@ -32,6 +32,12 @@ constexpr int BM = 128, BN = 128;
 constexpr int kThreads = 192;
 constexpr float LOG2E = 1.4426950408889634f, LN2 = 0.6931471805599453f;
 constexpr float RESCALE_THRESHOLD = 8.0f;  // in log2 units
+#ifndef ENC_ATTN_STAGGER
+#define ENC_ATTN_STAGGER 1000  // cycles
+#endif
+#ifndef ENC_ATTN_POLY
+#define ENC_ATTN_POLY 8  // one pair of exponentials in 8 goes to the FMA pipes (measured best among 0, 1/2, 1/4, 1/8)
+#endif
 
 struct AttnArgs {
     void *o;
@@ -54,27 +60,75 @@ struct AttnArgs {
 #define PROF_ADD(i) do {} while (0)
 #endif
 
+// 2^x on the FMA pipes, for the share of the exponentials that the special-function unit (16 results per
+// clock per SM) has no time for once two softmax warpgroups run side by side: x = i + f with i integer and f
+// in [-0.5, 0.5], 2^f by a cubic (max relative error 7.7e-5, below the bfloat16/float16 rounding of P), the
+// exponent field adjusted by i.  Inputs below -126 (masked scores) give 2^-126 instead of zero.  See
+// exp2_fma_pair below.
+
+// Packed float32 pairs: sm_100 executes fma / add on two float32 values in one instruction.
+__device__ __forceinline__ uint64_t f2_pack(float lo, float hi) {
+    uint64_t r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+    return r;
+}
+__device__ __forceinline__ void f2_unpack(uint64_t v, float &lo, float &hi) { asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v)); }
+__device__ __forceinline__ uint64_t f2_fma(uint64_t a, uint64_t b, uint64_t c) {
+    uint64_t d;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+    return d;
+}
+__device__ __forceinline__ uint64_t f2_add(uint64_t a, uint64_t b) {
+    uint64_t d;
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+    return d;
+}
+__device__ __forceinline__ float max3(float a, float b, float c) {
+    float d;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+    return d;
+}
+// 2^x for a pair of values on the FMA pipes
+__device__ __forceinline__ void exp2_fma_pair(float x0, float x1, float &p0, float &p1) {
+    const uint64_t x = f2_pack(fmaxf(x0, -126.0f), fmaxf(x1, -126.0f));
+    const uint64_t t = f2_add(x, f2_pack(12582912.0f, 12582912.0f));
+    const uint64_t f = f2_fma(f2_add(t, f2_pack(-12582912.0f, -12582912.0f)), f2_pack(-1.0f, -1.0f), x);
+    uint64_t p = f2_fma(f, f2_pack(0.05508868396282196f, 0.05508868396282196f), f2_pack(0.24260404706001282f, 0.24260404706001282f));
+    p = f2_fma(p, f, f2_pack(0.6932762265205383f, 0.6932762265205383f));
+    p = f2_fma(p, f, f2_pack(0.9999289512634277f, 0.9999289512634277f));
+    float t0, t1, q0, q1;
+    f2_unpack(t, t0, t1);
+    f2_unpack(p, q0, q1);
+    p0 = __uint_as_float(__float_as_uint(q0) + (__float_as_uint(t0) << 23));
+    p1 = __uint_as_float(__float_as_uint(q1) + (__float_as_uint(t1) << 23));
+}
+
 // One row of one score block, in registers: mask, running maximum with lazy rescale, probabilities in
 // place (float32 bit patterns), row sum.  `alpha` is the factor the accumulator must be scaled by (1 when
-// no rescale is due).
-__device__ __forceinline__ void softmax_row(uint32_t (&sv)[4][32], float qk_scale, bool need_mask, int64_t n0, int64_t row,
+// no rescale is due).  POLY_PAIRS = n: one pair of exponentials in n runs on the FMA pipes (0: none).
+template <int NCH, int POLY_PAIRS = 0>
+__device__ __forceinline__ void softmax_row(uint32_t (&sv)[NCH][32], float qk_scale, bool need_mask, int64_t n0, int64_t row,
                                             int64_t seq, int causal, float &m_ref, float &l, float &alpha, bool &rescale) {
     if (need_mask) {
 #pragma unroll
-        for (int c = 0; c < 4; ++c)
+        for (int c = 0; c < NCH; ++c)
 #pragma unroll
             for (int i = 0; i < 32; ++i) {
                 const int64_t col = n0 + c * 32 + i;
                 if (col >= seq || (causal && col > row)) sv[c][i] = __float_as_uint(-INFINITY);
             }
     }
-    // row maximum of the raw scores (the scale is positive, so it commutes with the maximum)
-    float mx = -INFINITY;
+    // row maximum of the raw scores (the scale is positive, so it commutes with the maximum); two chains of
+    // three-input maxima
+    float mx0 = -INFINITY, mx1 = -INFINITY;
 #pragma unroll
-    for (int c = 0; c < 4; ++c)
+    for (int c = 0; c < NCH; ++c)
 #pragma unroll
-        for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(sv[c][i]));
-    mx *= qk_scale;
+        for (int i = 0; i < 32; i += 4) {
+            mx0 = max3(mx0, __uint_as_float(sv[c][i]), __uint_as_float(sv[c][i + 1]));
+            mx1 = max3(mx1, __uint_as_float(sv[c][i + 2]), __uint_as_float(sv[c][i + 3]));
+        }
+    const float mx = fmaxf(mx0, mx1) * qk_scale;
     const float m_new = fmaxf(m_ref, mx);
     // rescale only when the maximum moved far enough for exp2(s - m_ref) to risk overflow
     rescale = m_new > m_ref + RESCALE_THRESHOLD;  // also true for the first finite maximum
@@ -84,22 +138,29 @@ __device__ __forceinline__ void softmax_row(uint32_t (&sv)[4][32], float qk_scal
         m_ref = m_new;
     }
     const float neg_m = m_ref == -INFINITY ? 0.0f : -m_ref;
-    // Evaluating part of the exponentials with a polynomial on the FMA pipes, and rounding P with integer
-    // operations, were both measured and both lost: a softmax warp is bound by its own instruction stream,
-    // not by the special-function unit, so extra instructions cost more than they free.
-    float sum0 = 0.0f, sum1 = 0.0f;  // two chains halve the dependent-add latency
+    const uint64_t scale2 = f2_pack(qk_scale, qk_scale), neg_m2 = f2_pack(neg_m, neg_m);
+    uint64_t sum0 = f2_pack(0.0f, 0.0f), sum1 = sum0;  // two chains of packed adds
 #pragma unroll
-    for (int c = 0; c < 4; ++c)
+    for (int c = 0; c < NCH; ++c)
 #pragma unroll
         for (int i = 0; i < 32; i += 2) {
-            const float p0 = fast_exp2(fmaf(__uint_as_float(sv[c][i]), qk_scale, neg_m));
-            const float p1 = fast_exp2(fmaf(__uint_as_float(sv[c][i + 1]), qk_scale, neg_m));
-            sum0 += p0;
-            sum1 += p1;
+            float x0, x1, p0, p1;
+            f2_unpack(f2_fma(f2_pack(__uint_as_float(sv[c][i]), __uint_as_float(sv[c][i + 1])), scale2, neg_m2), x0, x1);
+            if (POLY_PAIRS > 0 && ((c * 16 + (i >> 1)) % (POLY_PAIRS > 0 ? POLY_PAIRS : 1)) == POLY_PAIRS / 2) {
+                exp2_fma_pair(x0, x1, p0, p1);
+            } else {
+                p0 = fast_exp2(x0);
+                p1 = fast_exp2(x1);
+            }
+            const uint64_t p2 = f2_pack(p0, p1);
+            if (i & 2) sum1 = f2_add(sum1, p2);
+            else sum0 = f2_add(sum0, p2);
             sv[c][i] = __float_as_uint(p0);
             sv[c][i + 1] = __float_as_uint(p1);
         }
-    l = l * alpha + (sum0 + sum1);
+    float s0, s1;
+    f2_unpack(f2_add(sum0, sum1), s0, s1);
+    l = l * alpha + (s0 + s1);
 }
 
 // P row into shared memory in the swizzled K-major layout the MMA reads: 64-wide boxes, 128-byte rows,
@@ -651,6 +712,298 @@ attention_ts_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
     }
 }
 
+// ---- two query tiles per CTA, 64-key blocks, score products issued ahead ------------------------------------
+// With 128-key blocks the score buffer of a tile is also its P buffer, so S_t(j+1) has to follow P_t(j) V in
+// the MMA pipe and every softmax warpgroup idles for two matrix products per step.  With 64-key blocks a
+// tile's 128 score columns hold two buffers: S_t(j+1) goes into the other one while the softmax of block j
+// runs, P_t(j) overwrites the first 32 columns of its own buffer, and the tensor core never waits for a
+// softmax that has work queued.  A 128x64x16 MMA runs at two thirds of the rate of a 128x128x16 one, which
+// the removed idle time more than pays for.
+//   TMEM columns: tile t buffer b at t*128 + b*64 (S, then P in its first 32)   O0 [256,256+D)  O1 [384,384+D)
+//   warp 0 = TMA producer, warps 1 and 2 = score issuers of tile 0 and 1 (S_t(j) goes out as soon as K(j) is
+//   there and P_t(j-2) V has left the buffer), warp 3 = P V issuer of both tiles; K and V have a ring each
+constexpr int BN64 = 64;
+
+template <int D, int STAGES> struct AttnSmem64 {  // STAGES blocks in the K ring and as many in the V ring
+    static constexpr int QTILE = BM * D * 2;
+    static constexpr int TILE = BN64 * D * 2;  // one 64-key block of K or V
+    static constexpr int Q_OFF = 0;            // 2 query tiles
+    static constexpr int K_OFF = 2 * QTILE;
+    static constexpr int V_OFF = K_OFF + STAGES * TILE;
+    static constexpr int BAR_OFF = V_OFF + STAGES * TILE;
+    static constexpr int NBARS = 1 + 4 * STAGES + 12 + 1;  // q, k/v full/empty, (s_full, p_full, pv_done) x 2 tiles x 2 buffers, o
+    static constexpr int TOTAL = BAR_OFF + NBARS * 8 + 16;
+};
+
+template <typename T, int D, int STAGES>
+__global__ void __launch_bounds__(kThreads2, 1)
+attention_ts64_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
+                      const __grid_constant__ CUtensorMap tm_v, AttnArgs a) {
+    using L = AttnSmem64<D, STAGES>;
+    constexpr int BNK = BN64;
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
+    uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint64_t *q_full = reinterpret_cast<uint64_t *>(smem + L::BAR_OFF);
+    uint64_t *k_full = q_full + 1;
+    uint64_t *k_empty = k_full + STAGES;
+    uint64_t *v_full = k_empty + STAGES;
+    uint64_t *v_empty = v_full + STAGES;
+    uint64_t *s_full = v_empty + STAGES;  // [tile * 2 + buffer]
+    uint64_t *p_full = s_full + 4;
+    uint64_t *pv_done = p_full + 4;
+    uint64_t *o_full = pv_done + 4;
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(o_full + 1);
+    volatile uint32_t *abort = tmem_slot + 1;
+
+#ifdef ENC_ATTN_PROF
+    __shared__ long long prof_acc[16];
+    if (threadIdx.x < 16) prof_acc[threadIdx.x] = 0;
+#endif
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int qb = a.causal ? (int)(gridDim.x - 1 - blockIdx.x) : (int)blockIdx.x;  // heavy blocks first
+    const int bh = blockIdx.y;
+    const int64_t m0 = (int64_t)qb * (2 * BM);
+    int nkv_t[2];
+#pragma unroll
+    for (int t = 0; t < 2; ++t) {
+        const int64_t r0 = m0 + t * BM;
+        const int64_t hi = a.causal ? (r0 + BM < a.seq ? r0 + BM : a.seq) : a.seq;
+        nkv_t[t] = r0 < a.seq ? (int)((hi + BNK - 1) / BNK) : 0;
+    }
+    const int nkv = nkv_t[0] > nkv_t[1] ? nkv_t[0] : nkv_t[1];
+    constexpr uint32_t TMEM_COLS = 512;
+
+    if (threadIdx.x == 0) {
+        mbar_init(q_full, 1);
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(&k_full[s], 1);
+            mbar_init(&k_empty[s], 2);  // the score issuers of both tiles release a K block
+            mbar_init(&v_full[s], 1);
+            mbar_init(&v_empty[s], 1);
+        }
+        for (int i = 0; i < 4; ++i) {
+            mbar_init(&s_full[i], 1);
+            mbar_init(&p_full[i], 128);
+            mbar_init(&pv_done[i], 1);
+        }
+        mbar_init(o_full, 1);
+        *abort = 0;
+        fence_barrier_init();
+        prefetch_tensormap(&tm_q);
+        prefetch_tensormap(&tm_k);
+        prefetch_tensormap(&tm_v);
+    }
+    if (warp == 1) tmem_alloc(tmem_slot, TMEM_COLS);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp < 4) {
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 56;");
+        if (warp == 0 && lane == 0) {
+            // ---------------- TMA producer ----------------
+            mbar_expect_tx(q_full, 2 * L::QTILE);
+#pragma unroll
+            for (int t = 0; t < 2; ++t)
+#pragma unroll
+                for (int b = 0; b < D / 64; ++b)
+                    tma_load_3d(smem + L::Q_OFF + t * L::QTILE + b * (BM * 128), &tm_q, q_full, b * 64, (int)(m0 + t * BM), bh);
+            bool ok = true;
+            uint32_t ks = 0, kp = 0, vs = 0, vp = 0;  // ring positions
+            for (int it = 0; it < 2 * nkv && ok; ++it) {  // K0, K1 V0, K2 V1, ..., V(n-1): the order of consumption
+                const bool is_v = it == 2 * nkv - 1 || (it != 0 && (it & 1) == 0);
+                const int j = it == 0 ? 0 : it == 2 * nkv - 1 ? nkv - 1 : is_v ? (it - 2) >> 1 : (it + 1) >> 1;
+                uint32_t &st = is_v ? vs : ks, &ph = is_v ? vp : kp;
+                uint64_t *full = is_v ? &v_full[st] : &k_full[st];
+                ok = mbar_wait(is_v ? &v_empty[st] : &k_empty[st], ph ^ 1, abort);
+                if (!ok) break;
+                uint8_t *dst = smem + (is_v ? L::V_OFF : L::K_OFF) + st * L::TILE;
+                mbar_expect_tx(full, L::TILE);
+                const CUtensorMap *tm = is_v ? &tm_v : &tm_k;
+#pragma unroll
+                for (int b = 0; b < D / 64; ++b) tma_load_3d(dst + b * (BNK * 128), tm, full, b * 64, j * BNK, bh);
+                if (++st == STAGES) { st = 0; ph ^= 1; }
+            }
+            if (*abort) {  // drain our own copies before the CTA exits
+                for (uint32_t i = 0; i < (1u << 16) && !mbar_try_wait(q_full, 0); ++i) {}
+                for (uint32_t s = 0; s < (uint32_t)STAGES; ++s) {
+                    for (uint32_t i = 0; i < (1u << 16) && !mbar_try_wait(&k_full[s], s < ks ? kp : kp ^ 1); ++i) {}
+                    for (uint32_t i = 0; i < (1u << 16) && !mbar_try_wait(&v_full[s], s < vs ? vp : vp ^ 1); ++i) {}
+                }
+            }
+        } else if ((warp == 1 || warp == 2) && lane == 0) {
+            // ---------------- score issuers: warp 1 serves tile 0, warp 2 tile 1 ----------------
+            // An MMA costs its issuing thread 50-100 cycles next to the busy softmax warps, about what the tensor
+            // core needs to execute it, so the three matrix-product streams (S of either tile, P V of both) each
+            // get a thread on a scheduler of their own.  Both score issuers walk every K block, waiting for it and
+            // releasing it, so that the ring sees two arrivals per block whatever each tile needs.
+            const int t = warp - 1;
+            const int my_nkv = nkv_t[t];
+            const uint32_t idesc_s = idesc_f16(a.is_bf16, /*b_mn_major=*/false, BM, BNK);
+            bool ok = mbar_wait(q_full, 0, abort);
+            constexpr uint32_t desc_hi = smem_desc_hi_sw128(1024);
+            const uint32_t q_lo = smem_desc_lo(smem_u32(smem + L::Q_OFF + t * L::QTILE), 16);
+            const uint32_t k_lo = smem_desc_lo(smem_u32(smem + L::K_OFF), 16);
+            const uint32_t s_tmem = tmem_base + t * 128;
+            uint32_t stage = 0, phase = 0;
+            if (t == 1) {
+                // Start tile 1 about half a block period after tile 0, so that the two softmax warpgroups take
+                // turns on the special-function unit instead of meeting there; the offset then persists because
+                // both tiles do the same work per block.
+                const long long t_start = clock64();
+                while (clock64() - t_start < ENC_ATTN_STAGGER) {}
+            }
+            PROF_T0();
+            for (int j = 0; j < nkv && ok; ++j) {
+                ok = mbar_wait(&k_full[stage], phase, abort);
+                if (!ok) break;
+                if (t == 0) PROF_ADD(8);
+                if (j < my_nkv) {
+                    // buffer j & 1 held S_t(j-2), then P_t(j-2): free once P_t(j-2) V has completed
+                    if (j >= 2) ok = mbar_wait(&pv_done[t * 2 + (j & 1)], ((j - 2) >> 1) & 1, abort);
+                    if (!ok) break;
+                    tc_fence_after();
+                    if (t == 0) PROF_ADD(9);
+                    const uint32_t kb = k_lo + stage * (L::TILE >> 4);
+                    const uint32_t d_tmem = s_tmem + (j & 1) * BNK;
+#pragma unroll
+                    for (int kk = 0; kk < D / 16; ++kk)  // 64-wide boxes (128 query rows / 64 key rows each), then 32 bytes per step
+                        tc_mma_f16_halves(d_tmem, q_lo + (((kk >> 2) * (BM * 128) + (kk & 3) * 32) >> 4), desc_hi,
+                                          kb + (((kk >> 2) * (BNK * 128) + (kk & 3) * 32) >> 4), desc_hi, idesc_s, kk != 0);
+                    tc_commit(&s_full[t * 2 + (j & 1)]);
+                }
+                tc_commit(&k_empty[stage]);
+                if (++stage == STAGES) { stage = 0; phase ^= 1; }
+                if (t == 0) PROF_ADD(10);
+            }
+        } else if (warp == 3 && lane == 0) {
+            // ---------------- P V issuer, both tiles in turn ----------------
+            const uint32_t idesc_o = idesc_f16(a.is_bf16, /*b_mn_major=*/true, BM, D);
+            constexpr uint32_t desc_hi = smem_desc_hi_sw128(1024);
+            const uint32_t v_lo = smem_desc_lo(smem_u32(smem + L::V_OFF), BNK * 128);
+            uint32_t stage = 0, phase = 0;
+            bool ok = true;
+            PROF_T0();
+            for (int j = 0; j < nkv && ok; ++j) {
+                ok = mbar_wait(&v_full[stage], phase, abort);
+                if (!ok) break;
+                PROF_ADD(11);
+                const uint32_t vb = v_lo + stage * (L::TILE >> 4);
+#pragma unroll
+                for (int t = 0; t < 2; ++t) {
+                    if (j >= nkv_t[t]) continue;
+                    ok = mbar_wait(&p_full[t * 2 + (j & 1)], (j >> 1) & 1, abort);
+                    if (!ok) break;
+                    tc_fence_after();
+                    PROF_ADD(12 + t);
+                    const uint32_t p_tmem = tmem_base + t * 128 + (j & 1) * BNK;
+#pragma unroll
+                    for (int kk = 0; kk < BNK / 16; ++kk)  // 16 keys = 8 packed columns of P, 16 rows = 2048 bytes of V
+                        tc_mma_f16_ts_halves(tmem_base + 256 + t * 128, p_tmem + kk * 8, vb + kk * (2048 >> 4), desc_hi, idesc_o, (j | kk) != 0);
+                    tc_commit(&pv_done[t * 2 + (j & 1)]);
+                }
+                if (!ok) break;
+                tc_commit(&v_empty[stage]);
+                if (++stage == STAGES) { stage = 0; phase ^= 1; }
+                PROF_ADD(14);
+            }
+            if (ok) tc_commit(o_full);
+        }
+    } else {
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 224;");
+        // ---------------- softmax warpgroups: tile = warpgroup - 1 ----------------
+        const int t = (warp >> 2) - 1;
+        const int quarter = warp & 3;
+        const int r = quarter * 32 + lane;  // row inside the tile == TMEM lane
+        const int64_t row = m0 + t * BM + r;
+        const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
+        const uint32_t t_s = tmem_base + lane_addr + t * 128;
+        const uint32_t t_o = tmem_base + lane_addr + 256 + t * 128;
+        const int my_nkv = nkv_t[t];
+        const int64_t tile_m0 = m0 + t * BM;
+        float m_ref = -INFINITY, l = 0.0f;
+        bool ok = true;
+        PROF_T0();
+        for (int j = 0; j < my_nkv && ok; ++j) {
+            const int b = j & 1;
+            ok = mbar_wait(&s_full[t * 2 + b], (j >> 1) & 1, abort);
+            if (!ok) break;
+            tc_fence_after();
+            if (warp == 4) PROF_ADD(0);
+            const int64_t n0 = (int64_t)j * BNK;
+            const bool need_mask = (n0 + BNK > a.seq) || (a.causal && n0 + BNK > tile_m0);
+            uint32_t sv[2][32];
+#pragma unroll
+            for (int c = 0; c < 2; ++c) tmem_ld_32x32(t_s + b * BNK + c * 32, sv[c]);
+            tmem_ld_wait();
+            if (warp == 4) PROF_ADD(1);
+            float alpha;
+            bool rescale;
+            softmax_row<2, ENC_ATTN_POLY>(sv, a.qk_scale, need_mask, n0, row, a.seq, a.causal, m_ref, l, alpha, rescale);
+            if (warp == 4) PROF_ADD(2);
+            if (j > 0 && __any_sync(0xffffffffu, rescale)) {
+                // O_t must be quiescent: P_t(j-1) V complete (P_t(j) V is not issued before this thread's arrival below)
+                ok = mbar_wait(&pv_done[t * 2 + (b ^ 1)], ((j - 1) >> 1) & 1, abort);
+                if (!ok) break;
+                tc_fence_after();
+#pragma unroll 1
+                for (int c0 = 0; c0 < D; c0 += 32) {
+                    uint32_t v[32];
+                    tmem_ld_32x32(t_o + c0, v);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * alpha);
+                    tmem_st_32x32(t_o + c0, v);
+                }
+            }
+            // P_t(j), two values per column, over the first 32 columns of its own score buffer
+            uint32_t pk[32];
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {
+                const int e = 2 * i;
+                pk[i] = pack_pair<T>(__uint_as_float(sv[e >> 5][e & 31]), __uint_as_float(sv[e >> 5][(e & 31) + 1]));
+            }
+            tmem_st_32x32(t_s + b * BNK, pk);
+            tmem_st_wait();
+            tc_fence_before();
+            mbar_arrive(&p_full[t * 2 + b]);
+            if (warp == 4) PROF_ADD(4);
+        }
+        // ---- epilogue: O_t / l ----
+        if (ok && my_nkv > 0) ok = mbar_wait(o_full, 0, abort);
+        if (ok && my_nkv > 0) {
+            tc_fence_after();
+            T *o = reinterpret_cast<T *>(a.o) + (int64_t)bh * a.stride_h + row * a.stride_m;
+#pragma unroll 1
+            for (int c0 = 0; c0 < D; c0 += 32) {
+                uint32_t v[32];
+                tmem_ld_32x32(t_o + c0, v);
+                tmem_ld_wait();
+                if (row < a.seq) {
+                    float f[32];
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) f[i] = __fdiv_rn(__uint_as_float(v[i]), l);
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) *reinterpret_cast<uint4 *>(o + c0 + 8 * i) = Pack<T>::pack(f + 8 * i);
+                }
+            }
+            if (a.lse && row < a.seq) a.lse[(int64_t)bh * a.seq + row] = (m_ref + log2f(l)) * LN2;
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+#ifdef ENC_ATTN_PROF
+    if (threadIdx.x < 16 && a.prof) atomicAdd(a.prof + threadIdx.x, (unsigned long long)prof_acc[threadIdx.x]);
+#endif
+    if (threadIdx.x == 0 && *abort) atomicExch(a.error, 4u);
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, TMEM_COLS);
+    }
+}
+
 // ---- CUDA-core kernel: any head_dim <= 128, any of the three dtypes, any strides -------------------
 // One CTA of 128 threads per (batch*head, 16 query rows): 8 threads share a row and split head_dim.
 template <typename T>
@@ -733,22 +1086,23 @@ __global__ void __launch_bounds__(128) attention_simple_kernel(const T *q, const
     }
 }
 
-constexpr int ATTN_VARIANTS = 3;  // 0: two 128-row query tiles per CTA, P in TMEM; 1, 2: one tile, P through shared memory, 4- or 3-deep K/V ring
+constexpr int ATTN_VARIANTS = 4;  // 0: two 128-row query tiles per CTA, P in TMEM; 1, 2: one tile, P through shared memory, 4- or 3-deep K/V ring
 
-// Tensor maps over [bh, seq, D] with 64 x 128 boxes, then the launch.  TILES = query tiles of 128 rows per CTA.
-template <typename T, int D, int STAGES, int TILES>
+// Tensor maps over [bh, seq, D] with boxes of 64 values x 128 rows (64 rows for K and V when KV_ROWS is 64),
+// then the launch.  TILES = query tiles of 128 rows per CTA.
+template <typename T, int D, int STAGES, int TILES, int KV_ROWS = 128>
 int launch_tc(const void *q, const void *k, const void *v, const AttnArgs &args, int64_t bh, cudaStream_t st) {
     char err[256];
     CUtensorMap tq, tk, tv;
     const uint64_t dims[3] = {(uint64_t)D, (uint64_t)args.seq, (uint64_t)bh};
     const uint64_t strides[2] = {(uint64_t)args.stride_m * 2, (uint64_t)args.stride_h * 2};
-    const uint32_t box[3] = {64, BM, 1};
+    const uint32_t box[3] = {64, BM, 1}, kv_box[3] = {64, KV_ROWS, 1};
     if (!make_tensor_map(&tq, q, args.is_bf16, 3, dims, strides, box, err, sizeof(err)) ||
-        !make_tensor_map(&tk, k, args.is_bf16, 3, dims, strides, box, err, sizeof(err)) ||
-        !make_tensor_map(&tv, v, args.is_bf16, 3, dims, strides, box, err, sizeof(err)))
+        !make_tensor_map(&tk, k, args.is_bf16, 3, dims, strides, kv_box, err, sizeof(err)) ||
+        !make_tensor_map(&tv, v, args.is_bf16, 3, dims, strides, kv_box, err, sizeof(err)))
         return fail(ENC_ERR_LAUNCH, "enc_attention_fwd: %s", err);
-    auto kern = TILES == 2 ? attention_ts_kernel<T, D, STAGES> : attention_tc_kernel<T, D, STAGES>;
-    const int smem = (TILES == 2 ? AttnSmemTs<D, STAGES>::TOTAL : AttnSmem<D, STAGES>::TOTAL) + 1024;
+    auto kern = TILES == 1 ? attention_tc_kernel<T, D, STAGES> : KV_ROWS == 64 ? attention_ts64_kernel<T, D, STAGES> : attention_ts_kernel<T, D, STAGES>;
+    const int smem = (TILES == 1 ? AttnSmem<D, STAGES>::TOTAL : KV_ROWS == 64 ? AttnSmem64<D, STAGES>::TOTAL : AttnSmemTs<D, STAGES>::TOTAL) + 1024;
     const int threads = TILES == 2 ? kThreads2 : kThreads;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return fail(ENC_ERR_LAUNCH, "enc_attention_fwd: cannot opt in to %d bytes of shared memory: %s", smem, cudaGetErrorString(e));
@@ -760,9 +1114,13 @@ int launch_tc(const void *q, const void *k, const void *v, const AttnArgs &args,
     kern<<<grid, threads, smem, st>>>(tq, tk, tv, pa);
     cudaDeviceSynchronize();
     {
-        const double blocks = (double)grid.x * grid.y * (double)cdiv(args.seq, BN) * (args.causal ? 0.5 : 1.0);
+        const double blocks = (double)grid.x * grid.y * (double)cdiv(args.seq, KV_ROWS) * (args.causal ? 0.5 : 1.0);
         const char *names[15] = {"sm wait s_full", "sm load S", "sm max+exp", "", "sm rescale+store P", "", "", "",
                                  "mma wait V", "mma wait p_full0", "mma issue S0", "mma wait p_full1", "mma issue PV1 S1", "mma wait K", "mma issue PV0"};
+        if (KV_ROWS == 64) {
+            names[8] = "S0 wait K"; names[9] = "S0 wait pv_done"; names[10] = "S0 issue"; names[11] = "PV wait V"; names[12] = "PV wait P0";
+            names[13] = "PV issue 0 + wait P1"; names[14] = "PV issue 1";
+        }
         for (int i = 0; i < 15; ++i)
             if (pa.prof[i]) printf("  prof %-20s %9.0f cycles per kv block (tile 0)\n", names[i], (double)pa.prof[i] / blocks);
     }
@@ -790,12 +1148,14 @@ int launch_attention(const void *q, const void *k, const void *v, AttnArgs args,
     args.error = device_error_word();
     if (!args.error) return fail(ENC_ERR_NO_MEMORY, "enc_attention_fwd: cannot allocate the device status word");
     if constexpr (sizeof(T) == 2) {
-        if (variant < 0) variant = args.seq > BM ? 0 : 1;  // two tiles per CTA once there are two tiles
+        if (variant < 0) variant = args.seq > BM ? 3 : 1;  // two tiles per CTA once there are two tiles
         if (d == 128) {
             if (variant == 0) return launch_tc<T, 128, 5, 2>(q, k, v, args, bh, st);
+            if (variant == 3) return launch_tc<T, 128, 5, 2, 64>(q, k, v, args, bh, st);
             return variant == 2 ? launch_tc<T, 128, 3, 1>(q, k, v, args, bh, st) : launch_tc<T, 128, 4, 1>(q, k, v, args, bh, st);
         }
         if (variant == 0) return launch_tc<T, 64, 8, 2>(q, k, v, args, bh, st);
+        if (variant == 3) return launch_tc<T, 64, 6, 2, 64>(q, k, v, args, bh, st);
         return variant == 2 ? launch_tc<T, 64, 3, 1>(q, k, v, args, bh, st) : launch_tc<T, 64, 4, 1>(q, k, v, args, bh, st);
     }
     return fail(ENC_ERR_UNSUPPORTED, "enc_attention_fwd: unreachable");
@@ -806,6 +1166,7 @@ int launch_attention(const void *q, const void *k, const void *v, AttnArgs args,
 int attention_variants() { return ATTN_VARIANTS; }
 void attention_variant_info(int v, char *out, size_t n) {
     if (v == 0) snprintf(out, n, "block_m=256 (two 128-row tiles, one softmax warpgroup each) block_n=128 tcgen05 S/P/O in TMEM");
+    else if (v == 3) snprintf(out, n, "block_m=256 (two 128-row tiles) block_n=64 tcgen05 S/P/O in TMEM, score products issued one block ahead");
     else snprintf(out, n, "block_m=128 block_n=128 kv_stages=%d tcgen05 S/O in TMEM, P through shared memory", v == 2 ? 3 : 4);
 }
 
