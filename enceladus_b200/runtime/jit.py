@@ -24,6 +24,7 @@ from typing import Any
 import numpy as np
 
 from enceladus_b200 import language as tl
+from enceladus_b200 import _native as N
 from enceladus_b200.runtime import interop
 
 MAX_GRID = (2**31 - 1, 65535, 65535)
@@ -178,6 +179,80 @@ class JITFunction:
         ad = self.adapter()
         v = self.variant if variant is None else variant
         launch(ad, bound, g, -1 if v is None else int(v), self)
+
+    def warmup(self, *args: Any, grid: Any = None, num_warps: int = 4, dot_warps: tuple[int, int] | None = None,
+               dot_backend: str = "auto", variant: int | None = None, **kwargs: Any) -> CompiledKernel:
+        """Does everything a launch does short of launching: binds the arguments, finds the native kernel and
+        loads the library (src/enceladus/runtime/jit.py:527-537 compiles without launching; here the kernels
+        are compiled ahead of time, so the costs that remain are the library load and the symbol lookup).
+
+        Raises what a launch would raise for an unknown kernel, a bad binding or a missing library.
+        """
+        if num_warps not in (1, 2, 4, 8, 16, 32):
+            raise ValueError(f"num_warps must be a power of two from 1 to 32, but got {num_warps}")
+        self.bind(args, kwargs)
+        ad = self.adapter()
+        n = N.num_variants(ad.kernel_id)
+        v = self.variant if variant is None else variant
+        v = -1 if v is None else int(v)
+        if v >= n:
+            raise ValueError(f"{self.__name__}: variant {v} is out of range, the kernel has {n}")
+        return CompiledKernel(self.__name__, _ENTRY_POINTS[ad.kernel_id],
+                              tuple(N.variant_info(ad.kernel_id, i) for i in range(n)), v, num_warps)
+
+    def explain(self, *args: Any, grid: Any = None, num_warps: int = 4, dot_warps: tuple[int, int] | None = None,
+                dot_backend: str = "auto", variant: int | None = None, **kwargs: Any) -> str:
+        """Prints and returns what a launch with these arguments would run.
+
+        The reference reports tile layouts, register estimates and threadgroup memory of the code it
+        generates (src/enceladus/runtime/jit.py:539-573).  Nothing is generated here; the report names the
+        native entry point, the array arguments with their dtypes and shapes, and the tile variants with the
+        one in force.
+        """
+        ck = self.warmup(*args, num_warps=num_warps, dot_warps=dot_warps, dot_backend=dot_backend, variant=variant,
+                         **kwargs)
+        bound = self.bind(args, kwargs)
+        ad = self.adapter()
+        lines = [f"kernel {self.__name__} -> {ck.entry} (libenc_b200.so, precompiled for sm_100a)"]
+        if grid is not None:
+            lines.append(f"  grid {resolve_grid(grid, {k: (v.value if isinstance(v, tl.constexpr) else v) for k, v in bound.items()})}")
+        for name in ad.array_list:
+            a = bound[name]
+            role = "out" if name in ad.outputs else "in"
+            lines.append(f"  {role:3s} {name}: {getattr(a, 'dtype', type(a).__name__)} {tuple(getattr(a, 'shape', ()))}")
+        consts = {n: bound[n] for n in self._constexpr_names}
+        if consts:
+            lines.append("  constexpr " + ", ".join(f"{k}={v.value if isinstance(v, tl.constexpr) else v}" for k, v in consts.items()))
+        lines.append("  num_warps / dot_warps / dot_backend describe Apple SIMD-group layouts and are ignored")
+        for i, info in enumerate(ck.variants):
+            mark = "*" if i == ck.variant else " "
+            lines.append(f"  {mark} variant {i}: {info}")
+        if ck.variant < 0:
+            lines.append("  variant in force: chosen by the library from the shape")
+        text = "\n".join(lines)
+        print(text)
+        return text
+
+
+@dataclass(frozen=True)
+class CompiledKernel:
+    """What `JITFunction.warmup` returns: the precompiled native kernel a launch with these arguments uses.
+
+    The reference's object of the same name carries the generated MSL and IR
+    (src/enceladus/runtime/jit.py:527-537); nothing is generated here, so it names the native entry point
+    and lists the hand-written tile variants instead.
+    """
+
+    name: str
+    entry: str
+    variants: tuple[str, ...]
+    variant: int  # -1: the library chooses per shape
+    num_warps: int
+
+
+_ENTRY_POINTS = {N.K_SOFTMAX: "enc_softmax", N.K_LAYERNORM: "enc_layernorm", N.K_RMSNORM: "enc_rmsnorm",
+                 N.K_GELU: "enc_gelu", N.K_MATMUL: "enc_matmul", N.K_ATTENTION: "enc_attention_fwd",
+                 N.K_HISTOGRAM: "enc_histogram", N.K_CUMSUM: "enc_cumsum", N.K_ADD: "enc_add"}
 
 
 def launch(ad, bound: dict[str, Any], grid: tuple[int, int, int], variant: int, jf: JITFunction | None) -> None:

@@ -337,3 +337,23 @@ def test_two_rank_sharded_cumsum_and_histogram_over_gloo(tmp_path):
     for r, (p, out) in enumerate(zip(procs, outs)):
         assert p.returncode == 0, f"rank {r} failed:\n{out}"
         assert f"rank {r} ok" in out
+
+
+def test_warmup_and_explain_describe_the_native_kernel_without_launching(capsys):
+    """`kernel.warmup()` / `kernel.explain()` (reference: src/enceladus/runtime/jit.py:527-573) resolve the
+    native entry point and list the tile variants; neither needs a device."""
+    from enceladus_b200 import _native as N
+    from enceladus_b200 import ops
+
+    x = np.zeros((4, 8), np.float32)
+    ck = ops.softmax_kernel.warmup(x, x, 8, 8, 8, BLOCK=8)
+    assert ck.entry == "enc_softmax" and ck.variant == -1 and len(ck.variants) == N.num_variants(N.K_SOFTMAX)
+    q = np.zeros((1, 1, 128, 128), np.float16)
+    text = ops.attention_kernel.explain(q, q, q, q, 1.0, 128, 128 * 128, 128, HEAD_DIM=128, BLOCK_M=128, BLOCK_N=128,
+                                        CAUSAL=False, grid=(1, 1), variant=1)
+    assert text == capsys.readouterr().out.rstrip("\n")
+    assert "enc_attention_fwd" in text and "* variant 1" in text and "grid (1, 1, 1)" in text and "float16 (1, 1, 128, 128)" in text
+    with pytest.raises(ValueError, match="variant 99"):
+        ops.softmax_kernel.warmup(x, x, 8, 8, 8, BLOCK=8, variant=99)
+    with pytest.raises(TypeError):
+        ops.softmax_kernel.warmup(x, x, 8)
