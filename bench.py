@@ -393,7 +393,11 @@ def pinned(arrays):
     return tuple(out)
 
 
-def bench_workload(wl: dict, steps: int, warmup: int, pk: dict, pk_kind: str, sampler, e2e: bool, cpu: bool):
+def bench_workload(wl: dict, steps: int, warmup: int, pk: dict, pk_kind: str, sampler, e2e: bool, cpu: bool,
+                   min_region_ms: float = 0.0):
+    """One bench row.  `min_region_ms` > 0 (per-kernel rows only, never the headline) raises `steps` until the
+    timed region lasts about that long: a graph replay costs several microseconds to launch, which ten steps of
+    a 7-microsecond kernel do not amortise."""
     import torch
 
     nsets = wl.get("sets") or max(1, min(16, -(-ROTATE_BYTES // wl["set_bytes"])))
@@ -403,6 +407,16 @@ def bench_workload(wl: dict, steps: int, warmup: int, pk: dict, pk_kind: str, sa
     torch.cuda.synchronize()
     m0 = sampler.mark() if sampler else 0
     graph = USE_GRAPH and not (WORLD > 1 and wl["kernel"] in ("histogram", "cumsum"))  # collectives stay eager
+    if min_region_ms > 0:
+        wl["run"](sets[0])
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        wl["run"](sets[-1])
+        e1.record()
+        torch.cuda.synchronize()
+        est = max(max_over_ranks(e0.elapsed_time(e1)), 1e-3)
+        steps = max(steps, min(200, int(min_region_ms / est) + 1))
     ms = timed_region(wl["run"], sets, steps, warmup, graph)
     m1 = sampler.mark() if sampler else 0
     achieved = wl["work"] / (ms * 1e-3) / (1e9 if wl["unit"] == "GB/s" else 1e12)
@@ -564,8 +578,8 @@ def main() -> None:
         for k in names:
             try:
                 rows.append(bench_workload(W[k](), args.kernel_steps, 3, pk, pk_kind, sampler,
-                                           e2e=not args.no_e2e, cpu=args.cpu_baseline_all))
-                launches += args.kernel_steps
+                                           e2e=not args.no_e2e, cpu=args.cpu_baseline_all, min_region_ms=1.0))
+                launches += rows[-1]["steps"]
             except Exception as e:  # noqa: BLE001 - one failing workload must not hide the others
                 rows.append({"name": k, "error": f"{type(e).__name__}: {e}"})
     if sampler:

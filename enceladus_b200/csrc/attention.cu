@@ -1,25 +1,25 @@
 // Flash-attention forward on the tcgen05 tensor cores of sm_100a.
 //
-// One CTA per (batch*head, 128 query rows).  Keys and values stream through a TMA-fed ring of
-// 128-byte-swizzled shared memory in blocks of 128 rows; both matrix products run as tcgen05.mma with
-// float32 accumulators in tensor memory:
+// Three kernels share the arithmetic, which follows the reference kernel (examples/08_flash_attention.py:30-70):
+// scores scaled after the float32 dot, exp2 of (score - max) with scale * log2 e folded into one multiply,
+// P cast to the input dtype before the second dot, a true division by l at the end; masked with -inf outside
+// the sequence and above the diagonal.  The running output is rescaled only when the row maximum has grown by
+// more than 2^8 since the last rescale (the statistics stay exact: l and the final 1/l use the same reference
+// maximum).  lse = ln2 * (m + log2 l) when requested.  Causal launches skip key blocks above the diagonal.
+//
+//   attention_ts64_kernel  two 128-row query tiles per CTA, 64-key blocks, S / P / O in tensor memory, three
+//                          MMA-issuing threads (the default for sequences longer than one tile)
+//   attention_ts_kernel    the same with 128-key blocks and one MMA-issuing thread
+//   attention_tc_kernel    one 128-row tile per CTA, P through shared memory:
 //     S = Q K^T    (128 x 128, A = Q K-major, B = K block K-major)      -> TMEM, double buffered
 //     O += P V     (128 x D,   A = P K-major in shared memory, B = V block MN-major) -> TMEM
-//   warp 0      TMA producer (Q once, then K0, K1 V0, K2 V1, ... through the ring: the order of consumption)
-//   warp 1      MMA issuer; S of block j+1 is issued before P V of block j so that the tensor core
-//               works while the softmax warps are busy with block j
-//   warps 2..5  softmax: thread i owns query row i.  Base-2 online softmax in float32 on the scaled
-//               scores (scale * log2 e folded into one multiply), masked with -inf outside the sequence
-//               and above the diagonal; P is rounded to the input type and written to shared memory in
-//               the swizzled layout the MMA reads; the running output is rescaled in TMEM only when
-//               the row maximum has grown by more than 2^8 since the last rescale (the statistics stay
-//               exact: l and the final 1/l use the same reference maximum).  Finally O / l is stored,
-//               and lse = ln2 * (m + log2 l) when requested.
-// The arithmetic follows the reference kernel (examples/08_flash_attention.py:30-70): scores scaled
-// after the float32 dot, exp2 of (score - max), P cast to the input dtype before the second dot, a true
-// division by l at the end.  Causal launches skip key blocks above the diagonal.
+//     warp 0      TMA producer (Q once, then K0, K1 V0, K2 V1, ... through the ring: the order of consumption)
+//     warp 1      MMA issuer; S of block j+1 is issued before P V of block j so that the tensor core
+//                 works while the softmax warps are busy with block j
+//     warps 2..5  softmax: thread i owns query row i; P is written to shared memory in the swizzled layout
+//                 the MMA reads
 //
-// Shapes this kernel does not take (head_dim other than 64/128, float32 inputs, strides that TMA
+// Shapes these kernels do not take (head_dim other than 64/128, float32 inputs, strides that TMA
 // cannot describe) run on a CUDA-core kernel with the same arithmetic.
 #include "sm100.cuh"
 
