@@ -3,7 +3,8 @@
 // Persistent, warp-specialised kernel, one CTA per SM:
 //   warp 0      TMA producer: cp.async.bulk.tensor tiles of A (128 x 64, K contiguous) and B (64 x BN,
 //               N contiguous, as BN/64 boxes of 64 x 64) into a STAGES-deep ring of 128-byte-swizzled
-//               shared memory, completion counted in bytes on the stage's "full" mbarrier.
+//               shared memory, completion counted in bytes on the stage's "full" mbarrier.  (Prefetching
+//               later K blocks into L2 with cp.async.bulk.prefetch.tensor was measured: 20% slower.)
 //   warp 1      MMA issuer: one elected thread issues tcgen05.mma (128 x BN x 16 per instruction, fp16 or
 //               bf16 operands straight from shared memory through matrix descriptors, float32
 //               accumulators in tensor memory); tcgen05.commit releases the stage ("empty" mbarrier) and,
@@ -34,6 +35,7 @@ struct MatmulArgs {
     int64_t M, N, K, ldc;
     int epilogue;
     int is_bf16;
+    int b_3d;  // the B tensor map is [N/64][K][64]: one copy per stage instead of BN/64
     unsigned *error;
 };
 
@@ -118,9 +120,13 @@ matmul_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
                     uint8_t *sb = sa + L::A_BYTES;
                     mbar_expect_tx(&full[stage], L::STAGE_BYTES);
                     tma_load_2d(sa, &tm_a, &full[stage], k * BK, mb * BM);
+                    if (a.b_3d) {  // one copy: the BN/64 boxes of 64 columns land BK*128 bytes apart, as below
+                        tma_load_3d(sb, &tm_b, &full[stage], 0, k * BK, nb * (BN / 64));
+                    } else {
 #pragma unroll
-                    for (int j = 0; j < BN / 64; ++j)
-                        tma_load_2d(sb + j * (BK * 128), &tm_b, &full[stage], nb * BN + j * 64, k * BK);
+                        for (int j = 0; j < BN / 64; ++j)
+                            tma_load_2d(sb + j * (BK * 128), &tm_b, &full[stage], nb * BN + j * 64, k * BK);
+                    }
                     if (++stage == STAGES) { stage = 0; phase ^= 1; }
                 }
             }
@@ -280,11 +286,22 @@ int launch_tc(const void *A, const void *B, const MatmulArgs &args, int64_t lda,
     CUtensorMap tm_a, tm_b;
     const uint64_t da[2] = {(uint64_t)args.K, (uint64_t)args.M}, sa[1] = {(uint64_t)lda * 2};
     const uint32_t ba[2] = {BK, BM};
-    const uint64_t db[2] = {(uint64_t)args.N, (uint64_t)args.K}, sb[1] = {(uint64_t)ldb * 2};
-    const uint32_t bb[2] = {64, BK};
-    if (!make_tensor_map(&tm_a, A, args.is_bf16, 2, da, sa, ba, err, sizeof(err)) ||
-        !make_tensor_map(&tm_b, B, args.is_bf16, 2, db, sb, bb, err, sizeof(err)))
-        return fail(ENC_ERR_LAUNCH, "enc_matmul: %s", err);
+    // B [K, N] row-major.  When N is a multiple of 64 it is described as [N/64][K][64], so that one copy brings
+    // all BN/64 column boxes of a stage (every TMA instruction costs the producer thread tens of cycles);
+    // otherwise as [K][N] with one copy per 64-column box (the ragged last box is zero-filled).
+    MatmulArgs largs = args;
+    largs.b_3d = args.N % 64 == 0;
+    bool ok = make_tensor_map(&tm_a, A, args.is_bf16, 2, da, sa, ba, err, sizeof(err));
+    if (ok && largs.b_3d) {
+        const uint64_t db[3] = {64, (uint64_t)args.K, (uint64_t)(args.N / 64)}, sb[2] = {(uint64_t)ldb * 2, 128};
+        const uint32_t bb[3] = {64, BK, BN / 64};
+        ok = make_tensor_map(&tm_b, B, args.is_bf16, 3, db, sb, bb, err, sizeof(err));
+    } else if (ok) {
+        const uint64_t db[2] = {(uint64_t)args.N, (uint64_t)args.K}, sb[1] = {(uint64_t)ldb * 2};
+        const uint32_t bb[2] = {64, BK};
+        ok = make_tensor_map(&tm_b, B, args.is_bf16, 2, db, sb, bb, err, sizeof(err));
+    }
+    if (!ok) return fail(ENC_ERR_LAUNCH, "enc_matmul: %s", err);
     auto kern = matmul_tc_kernel<T, BN, STAGES>;
     const int smem = L::TOTAL + 1024;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
@@ -292,7 +309,7 @@ int launch_tc(const void *A, const void *B, const MatmulArgs &args, int64_t lda,
     const int64_t tiles = cdiv(args.M, BM) * cdiv(args.N, BN);
     int64_t grid = device_props().sm_count;
     if (grid > tiles) grid = tiles;
-    kern<<<(unsigned)grid, kThreads, smem, st>>>(tm_a, tm_b, args);
+    kern<<<(unsigned)grid, kThreads, smem, st>>>(tm_a, tm_b, largs);
     return check_launch("enc_matmul");
 }
 
@@ -339,7 +356,7 @@ extern "C" int enc_matmul(const void *a, const void *b, const void *bias, void *
     if (lda < K || ldb < N || ldc < N) return enc::fail(ENC_ERR_BAD_ARG, "enc_matmul: a leading dimension is smaller than its row");
     if (variant >= enc::MATMUL_VARIANTS) return enc::fail(ENC_ERR_BAD_ARG, "enc_matmul: variant %d out of range", variant);
     if (K == 0) return enc::fail(ENC_ERR_UNSUPPORTED, "enc_matmul: K == 0");
-    enc::MatmulArgs args{bias, c, M, N, K, ldc, epilogue, dtype == ENC_BF16 ? 1 : 0, nullptr};
+    enc::MatmulArgs args{bias, c, M, N, K, ldc, epilogue, dtype == ENC_BF16 ? 1 : 0, 0, nullptr};
     cudaStream_t st = enc::as_stream(stream);
     switch (dtype) {
         case ENC_F16: return enc::launch_matmul<__half>(a, b, args, lda, ldb, variant, st);
