@@ -218,6 +218,12 @@ class Staged:
             raise ValueError(f"argument `{name}` is a read-only NumPy array, but the kernel writes it")
         if any(s < 0 for s in a.strides):
             raise ValueError(f"argument `{name}` has a negative stride, which kernels can't address")
+        if not a.flags.c_contiguous and a.size:
+            # A view with strided rows or other gaps: the kernel addresses it with the host strides, so the
+            # device copy must keep them.  Stage the whole span from the first to the last element.
+            span = sum((n - 1) * st for n, st in zip(a.shape, a.strides)) // a.itemsize + 1
+            a = np.lib.stride_tricks.as_strided(a, shape=(span,), strides=(a.itemsize,), writeable=a.flags.writeable)
+            overwritten = False
         host = _np_as_torch_view(a)
         if written and overwritten:
             dev = torch.empty_like(host, device="cuda")  # every element is produced by the kernel

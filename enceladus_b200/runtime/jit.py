@@ -281,6 +281,14 @@ def launch(ad, bound: dict[str, Any], grid: tuple[int, int, int], variant: int, 
         else:
             ad.fn(bound, grid, variant, interop.current_stream())
         return
+    if dev is not None and dev.index != torch.cuda.current_device():
+        raise ValueError("NumPy arguments are staged on the current CUDA device, but the tensor arguments "
+                         f"live on {dev}; make it current with torch.cuda.set_device first")
+    if ad.split is not None and not interop.async_numpy_enabled():
+        plan = _pipeline_plan(ad, bound, grid, host_names)
+        if plan is not None:
+            _launch_pipelined(ad, bound, grid, variant, jf, host_names, *plan)
+            return
     staged = interop.Staged()
     resolved = dict(bound)
     extents = ad.extents(bound, grid) if ad.extents is not None else {}
@@ -288,13 +296,101 @@ def launch(ad, bound: dict[str, Any], grid: tuple[int, int, int], variant: int, 
         v = bound[name]
         dense = v.flags.c_contiguous and extents.get(name) == v.size
         resolved[name] = staged.to_device(name, v, name in ad.outputs, overwritten=dense)
-    if dev is not None and dev.index != torch.cuda.current_device():
-        raise ValueError("NumPy arguments are staged on the current CUDA device, but the tensor arguments "
-                         f"live on {dev}; make it current with torch.cuda.set_device first")
     ad.fn(resolved, grid, variant, interop.current_stream())
     staged.finish()
     if jf is not None:
         jf.last_launch = {"h2d_bytes": staged.h2d_bytes, "d2h_bytes": staged.d2h_bytes, "variant": variant}
+
+
+PIPELINE_MIN_BYTES = 16 << 20   # below this much partitioned host data a launch is staged in one piece
+PIPELINE_PIECE_BYTES = 32 << 20  # target size of a piece, inputs and outputs together (measured best of 16-128 MB)
+PIPELINE_STREAMS = 3
+_side_streams: dict[int, list[Any]] = {}
+
+
+def _pipeline_plan(ad, bound: dict[str, Any], grid: tuple[int, int, int], host_names: list[str]):
+    """Decides whether a launch with NumPy arguments is staged piecewise; returns (split, pieces) or None.
+
+    Every partitioned array must be a C-contiguous NumPy array (its flat view is then a view), every piece
+    must start on a 256-byte boundary in every array (the kernels' vector paths need 16), and there must be
+    enough data for the overlap to pay for the extra launches.
+    """
+    sp = ad.split(bound, grid)
+    if sp is None or sp.units < 2:
+        return None
+    total = 0
+    align = 1  # pieces start at multiples of this many units
+    for name, per in sp.arrays.items():
+        v = bound[name]
+        if not isinstance(v, np.ndarray) or not v.flags.c_contiguous or per <= 0:
+            return None
+        total += min(v.size, sp.units * per) * v.itemsize
+        step = per * v.itemsize
+        need = 256 // np.gcd(256, step)
+        align = align * need // np.gcd(align, need)
+    if any(n not in sp.arrays and isinstance(bound[n], np.ndarray) and n in ad.outputs for n in host_names):
+        return None  # a shared output would be written by every piece
+    if total < PIPELINE_MIN_BYTES:
+        return None
+    pieces = int(max(2, min(32, total // PIPELINE_PIECE_BYTES)))
+    per_piece = -(-sp.units // pieces)
+    per_piece = -(-per_piece // align) * align
+    if per_piece >= sp.units:
+        return None
+    return sp, [(u0, min(per_piece, sp.units - u0)) for u0 in range(0, sp.units, per_piece)]
+
+
+def _launch_pipelined(ad, bound, grid, variant, jf, host_names, sp, pieces) -> None:
+    """Stages, runs and copies back one piece after the other on a few side streams, then waits for all of
+    them: the launch is complete when this returns, as the one-piece path is."""
+    torch = interop._torch()
+    cur = torch.cuda.current_stream()
+    di = torch.cuda.current_device()
+    streams = _side_streams.get(di)
+    if streams is None:
+        streams = _side_streams[di] = [torch.cuda.Stream() for _ in range(PIPELINE_STREAMS)]
+    staged = interop.Staged()
+    shared = dict(bound)
+    for name in host_names:
+        if name not in sp.arrays:
+            shared[name] = staged.to_device(name, bound[name], False)
+    ready = cur.record_event()
+    extents = ad.extents(bound, grid) if ad.extents is not None else {}
+    flat = {name: bound[name].reshape(-1) for name in sp.arrays}
+    dense = {name: extents.get(name) == bound[name].size for name in sp.arrays}
+    late: list[tuple[Any, Any]] = []
+    try:
+        for i, (u0, n) in enumerate(pieces):
+            st = streams[i % len(streams)]
+            if i < len(streams):
+                st.wait_event(ready)
+            with torch.cuda.stream(st):
+                piece = dict(shared)
+                piece.update(sp.rebind(n))
+                views = []
+                for name, per in sp.arrays.items():
+                    host = flat[name][u0 * per : min((u0 + n) * per, flat[name].size)]
+                    written = name in ad.outputs
+                    piece[name] = staged.to_device(name, host, written, overwritten=dense[name])
+                    if written:
+                        views.append((piece[name], host))
+                ad.fn(piece, sp.grid(n), variant, int(st.cuda_stream))
+                for d, host in views:
+                    hv = interop._np_as_torch_view(host)
+                    if hv.is_pinned():
+                        hv.copy_(d, non_blocking=True)
+                    else:  # a copy into pageable memory blocks the host until the stream gets there: do it last
+                        late.append((hv, d))
+                    staged.d2h_bytes += host.nbytes
+    finally:
+        for st in streams:
+            st.synchronize()
+    for hv, d in late:
+        hv.copy_(d)
+    staged.writeback.clear()
+    if jf is not None:
+        jf.last_launch = {"h2d_bytes": staged.h2d_bytes, "d2h_bytes": staged.d2h_bytes, "variant": variant,
+                          "pieces": len(pieces)}
 
 
 def jit(fn: Callable[..., Any] | None = None, *, interpret: bool | None = None,

@@ -19,6 +19,22 @@ from enceladus_b200.runtime import interop
 
 
 @dataclass
+class Split:
+    """How a launch can be cut into independent pieces (rows, elements, M-blocks, (batch, head) slices).
+
+    Used for NumPy arguments only: the launcher stages, runs and copies back one piece after the other on
+    a few streams, so that the host-to-device copy of piece i+1, the kernel of piece i and the
+    device-to-host copy of piece i-1 overlap (PCIe carries both directions at once).  Arrays that are not
+    listed are shared by all pieces and staged once.
+    """
+
+    units: int                                   # independent units in the launch
+    arrays: dict[str, int]                       # partitioned array -> elements per unit in its flat view
+    grid: Callable[[int], tuple[int, int, int]]  # units in a piece -> grid of its launch
+    rebind: Callable[[int], dict[str, Any]] = field(default=lambda n: {})  # units in a piece -> changed scalars
+
+
+@dataclass
 class Adapter:
     name: str
     params: tuple[str, ...]
@@ -29,6 +45,8 @@ class Adapter:
     # name -> number of elements the kernel writes into that output when it is laid out densely; a NumPy
     # output of exactly that size is fully overwritten, so its old contents need not be copied in
     extents: Callable[[dict[str, Any], tuple[int, int, int]], dict[str, int]] | None = field(repr=False, default=None)
+    # how to cut a launch into independent pieces, or None when the kernel has no such cut
+    split: Callable[[dict[str, Any], tuple[int, int, int]], Split | None] | None = field(repr=False, default=None)
 
     def __post_init__(self) -> None:
         self.array_list = tuple(p for p in self.params if p in self.arrays)
@@ -40,10 +58,10 @@ class Adapter:
 _REGISTRY: dict[str, Adapter] = {}
 
 
-def register(name: str, params: str, arrays: str, outputs: str, kernel_id: int, extents=None):
+def register(name: str, params: str, arrays: str, outputs: str, kernel_id: int, extents=None, split=None):
     def deco(fn):
         _REGISTRY[name] = Adapter(name, tuple(params.split()), frozenset(arrays.split()),
-                                  frozenset(outputs.split()), kernel_id, fn, extents)
+                                  frozenset(outputs.split()), kernel_id, fn, extents, split)
         return fn
 
     return deco
@@ -91,7 +109,8 @@ def _covers(what: str, have: int, need: int) -> None:
 # ---- softmax_kernel(out_ptr, in_ptr, stride_in, stride_out, n_cols, BLOCK) -------------------------
 @register("softmax_kernel", "out_ptr in_ptr stride_in stride_out n_cols BLOCK", "out_ptr in_ptr", "out_ptr",
           N.K_SOFTMAX,
-          extents=lambda a, g: {"out_ptr": g[0] * int(a["n_cols"])} if int(a["stride_out"]) == int(a["n_cols"]) else {})
+          extents=lambda a, g: {"out_ptr": g[0] * int(a["n_cols"])} if int(a["stride_out"]) == int(a["n_cols"]) else {},
+          split=lambda a, g: Split(g[0], {"in_ptr": int(a["stride_in"]), "out_ptr": int(a["stride_out"])}, lambda n: (n, 1, 1)))
 def _softmax(a, grid, variant, stream):
     _covers("softmax_kernel BLOCK", int(a["BLOCK"]), int(a["n_cols"]))
     dt = _same_dtype(a, "out_ptr", "in_ptr")
@@ -102,7 +121,9 @@ def _softmax(a, grid, variant, stream):
 # ---- layernorm_kernel(x, y, w, b, mean, rstd, stride_x, stride_y, n_cols, eps, BLOCK) --------------
 @register("layernorm_kernel", "x_ptr y_ptr w_ptr b_ptr mean_ptr rstd_ptr stride_x stride_y n_cols eps BLOCK",
           "x_ptr y_ptr w_ptr b_ptr mean_ptr rstd_ptr", "y_ptr mean_ptr rstd_ptr", N.K_LAYERNORM,
-          extents=lambda a, g: {"mean_ptr": g[0], "rstd_ptr": g[0], **({"y_ptr": g[0] * int(a["n_cols"])} if int(a["stride_y"]) == int(a["n_cols"]) else {})})
+          extents=lambda a, g: {"mean_ptr": g[0], "rstd_ptr": g[0], **({"y_ptr": g[0] * int(a["n_cols"])} if int(a["stride_y"]) == int(a["n_cols"]) else {})},
+          split=lambda a, g: Split(g[0], {"x_ptr": int(a["stride_x"]), "y_ptr": int(a["stride_y"]), "mean_ptr": 1, "rstd_ptr": 1},
+                                   lambda n: (n, 1, 1)))
 def _layernorm(a, grid, variant, stream):
     dt = _same_dtype(a, "x_ptr", "y_ptr", "w_ptr", "b_ptr")
     for n in ("mean_ptr", "rstd_ptr"):
@@ -116,7 +137,8 @@ def _layernorm(a, grid, variant, stream):
 # ---- rmsnorm_kernel(x, w, out, stride_x, stride_out, n_cols, eps, BLOCK) --------------------------
 @register("rmsnorm_kernel", "x_ptr w_ptr out_ptr stride_x stride_out n_cols eps BLOCK", "x_ptr w_ptr out_ptr",
           "out_ptr", N.K_RMSNORM,
-          extents=lambda a, g: {"out_ptr": g[0] * int(a["n_cols"])} if int(a["stride_out"]) == int(a["n_cols"]) else {})
+          extents=lambda a, g: {"out_ptr": g[0] * int(a["n_cols"])} if int(a["stride_out"]) == int(a["n_cols"]) else {},
+          split=lambda a, g: Split(g[0], {"x_ptr": int(a["stride_x"]), "out_ptr": int(a["stride_out"])}, lambda n: (n, 1, 1)))
 def _rmsnorm(a, grid, variant, stream):
     _covers("rmsnorm_kernel BLOCK", int(a["BLOCK"]), int(a["n_cols"]))
     dt = _same_dtype(a, "x_ptr", "w_ptr", "out_ptr")
@@ -127,7 +149,11 @@ def _rmsnorm(a, grid, variant, stream):
 # ---- fused_gelu_kernel(x, bias, out, n, n_cols, scale, BLOCK) -------------------------------------
 @register("fused_gelu_kernel", "x_ptr bias_ptr out_ptr n n_cols scale BLOCK", "x_ptr bias_ptr out_ptr", "out_ptr",
           N.K_GELU,
-          extents=lambda a, g: {"out_ptr": int(a["n"])})
+          extents=lambda a, g: {"out_ptr": int(a["n"])},
+          # whole rows of n_cols per piece, so that the bias index (i mod n_cols) is unchanged
+          split=lambda a, g: Split(int(a["n"]) // int(a["n_cols"]), {"x_ptr": int(a["n_cols"]), "out_ptr": int(a["n_cols"])},
+                                   lambda n: (-(-n * int(a["n_cols"]) // int(a["BLOCK"])), 1, 1),
+                                   lambda n: {"n": n * int(a["n_cols"])}) if int(a["n_cols"]) > 0 and int(a["n"]) % int(a["n_cols"]) == 0 else None)
 def _fused_gelu(a, grid, variant, stream):
     n = int(a["n"])
     _covers("fused_gelu_kernel grid*BLOCK", grid[0] * int(a["BLOCK"]), n)
@@ -138,7 +164,9 @@ def _fused_gelu(a, grid, variant, stream):
 
 # ---- tanh_gelu_kernel(x, out, n, BLOCK): the tanh form of benchmark config 2 ----------------------
 @register("tanh_gelu_kernel", "x_ptr out_ptr n BLOCK", "x_ptr out_ptr", "out_ptr", N.K_GELU,
-          extents=lambda a, g: {"out_ptr": int(a["n"])})
+          extents=lambda a, g: {"out_ptr": int(a["n"])},
+          split=lambda a, g: Split(int(a["n"]), {"x_ptr": 1, "out_ptr": 1}, lambda n: (-(-n // int(a["BLOCK"])), 1, 1),
+                                   lambda n: {"n": n}))
 def _tanh_gelu(a, grid, variant, stream):
     n = int(a["n"])
     _covers("tanh_gelu_kernel grid*BLOCK", grid[0] * int(a["BLOCK"]), n)
@@ -148,7 +176,9 @@ def _tanh_gelu(a, grid, variant, stream):
 
 # ---- add_kernel(x, y, out, n, BLOCK) -------------------------------------------------------------
 @register("add_kernel", "x_ptr y_ptr out_ptr n BLOCK", "x_ptr y_ptr out_ptr", "out_ptr", N.K_ADD,
-          extents=lambda a, g: {"out_ptr": int(a["n"])})
+          extents=lambda a, g: {"out_ptr": int(a["n"])},
+          split=lambda a, g: Split(int(a["n"]), {"x_ptr": 1, "y_ptr": 1, "out_ptr": 1}, lambda n: (-(-n // int(a["BLOCK"])), 1, 1),
+                                   lambda n: {"n": n}))
 def _add(a, grid, variant, stream):
     n = int(a["n"])
     _covers("add_kernel grid*BLOCK", grid[0] * int(a["BLOCK"]), n)
@@ -189,6 +219,12 @@ def _cumsum(a, grid, variant, stream):
 
 
 # ---- matmul kernels -------------------------------------------------------------------------------
+def _matmul_split(a, g):
+    """Pieces of whole rows of A and C; B (and the bias) are shared."""
+    return Split(int(a["M"]), {"a_ptr": int(a["stride_am"]), "c_ptr": int(a["stride_cm"])},
+                 lambda n: (g[0], -(-n // int(a["BM"])), 1), lambda n: {"M": n})
+
+
 def _matmul_common(a, grid, variant, stream, bias, epilogue):
     m, n, k = int(a["M"]), int(a["N"]), int(a["K"])
     _covers("matmul grid[0]*BN", grid[0] * int(a["BN"]), n)
@@ -202,14 +238,16 @@ def _matmul_common(a, grid, variant, stream, bias, epilogue):
 
 @register("matmul_bias_gelu_kernel", "a_ptr b_ptr bias_ptr c_ptr M N K stride_am stride_bk stride_cm BM BN BK",
           "a_ptr b_ptr bias_ptr c_ptr", "c_ptr", N.K_MATMUL,
-          extents=lambda a, g: {"c_ptr": int(a["M"]) * int(a["N"])} if int(a["stride_cm"]) == int(a["N"]) else {})
+          extents=lambda a, g: {"c_ptr": int(a["M"]) * int(a["N"])} if int(a["stride_cm"]) == int(a["N"]) else {},
+          split=_matmul_split)
 def _matmul_bias_gelu(a, grid, variant, stream):
     _matmul_common(a, grid, variant, stream, bias=True, epilogue=1)
 
 
 @register("matmul_desc_kernel", "a_ptr b_ptr c_ptr M N K stride_am stride_bk stride_cm BM BN BK",
           "a_ptr b_ptr c_ptr", "c_ptr", N.K_MATMUL,
-          extents=lambda a, g: {"c_ptr": int(a["M"]) * int(a["N"])} if int(a["stride_cm"]) == int(a["N"]) else {})
+          extents=lambda a, g: {"c_ptr": int(a["M"]) * int(a["N"])} if int(a["stride_cm"]) == int(a["N"]) else {},
+          split=_matmul_split)
 def _matmul_desc(a, grid, variant, stream):
     _matmul_common(a, grid, variant, stream, bias=False, epilogue=0)
 
@@ -217,7 +255,8 @@ def _matmul_desc(a, grid, variant, stream):
 @register("matmul_kernel",
           "a_ptr b_ptr c_ptr M N K stride_am stride_ak stride_bk stride_bn stride_cm stride_cn BM BN BK",
           "a_ptr b_ptr c_ptr", "c_ptr", N.K_MATMUL,
-          extents=lambda a, g: {"c_ptr": int(a["M"]) * int(a["N"])} if int(a["stride_cm"]) == int(a["N"]) else {})
+          extents=lambda a, g: {"c_ptr": int(a["M"]) * int(a["N"])} if int(a["stride_cm"]) == int(a["N"]) else {},
+          split=_matmul_split)
 def _matmul_ptr(a, grid, variant, stream):
     for s in ("stride_ak", "stride_bn", "stride_cn"):
         if int(a[s]) != 1:
@@ -229,7 +268,8 @@ def _matmul_ptr(a, grid, variant, stream):
 @register("attention_kernel",
           "q_ptr k_ptr v_ptr o_ptr sm_scale N_CTX stride_h stride_m HEAD_DIM BLOCK_M BLOCK_N CAUSAL",
           "q_ptr k_ptr v_ptr o_ptr", "o_ptr", N.K_ATTENTION,
-          extents=lambda a, g: {"o_ptr": g[1] * int(a["N_CTX"]) * int(a["HEAD_DIM"]), "lse_ptr": g[1] * int(a["N_CTX"])} if int(a["stride_m"]) == int(a["HEAD_DIM"]) and int(a["stride_h"]) == int(a["N_CTX"]) * int(a["HEAD_DIM"]) else {})
+          extents=lambda a, g: {"o_ptr": g[1] * int(a["N_CTX"]) * int(a["HEAD_DIM"]), "lse_ptr": g[1] * int(a["N_CTX"])} if int(a["stride_m"]) == int(a["HEAD_DIM"]) and int(a["stride_h"]) == int(a["N_CTX"]) * int(a["HEAD_DIM"]) else {},
+          split=lambda a, g: Split(g[1], {n: int(a["stride_h"]) for n in ("q_ptr", "k_ptr", "v_ptr", "o_ptr")}, lambda n: (g[0], n, 1)))
 def _attention(a, grid, variant, stream):
     s = int(a["N_CTX"])
     _covers("attention_kernel grid[0]*BLOCK_M", grid[0] * int(a["BLOCK_M"]), s)
@@ -243,7 +283,9 @@ def _attention(a, grid, variant, stream):
 @register("attention_lse_kernel",
           "q_ptr k_ptr v_ptr o_ptr lse_ptr sm_scale N_CTX stride_h stride_m HEAD_DIM BLOCK_M BLOCK_N CAUSAL",
           "q_ptr k_ptr v_ptr o_ptr lse_ptr", "o_ptr lse_ptr", N.K_ATTENTION,
-          extents=lambda a, g: {"o_ptr": g[1] * int(a["N_CTX"]) * int(a["HEAD_DIM"]), "lse_ptr": g[1] * int(a["N_CTX"])} if int(a["stride_m"]) == int(a["HEAD_DIM"]) and int(a["stride_h"]) == int(a["N_CTX"]) * int(a["HEAD_DIM"]) else {})
+          extents=lambda a, g: {"o_ptr": g[1] * int(a["N_CTX"]) * int(a["HEAD_DIM"]), "lse_ptr": g[1] * int(a["N_CTX"])} if int(a["stride_m"]) == int(a["HEAD_DIM"]) and int(a["stride_h"]) == int(a["N_CTX"]) * int(a["HEAD_DIM"]) else {},
+          split=lambda a, g: Split(g[1], {**{n: int(a["stride_h"]) for n in ("q_ptr", "k_ptr", "v_ptr", "o_ptr")}, "lse_ptr": int(a["N_CTX"])},
+                                   lambda n: (g[0], n, 1)))
 def _attention_lse(a, grid, variant, stream):
     s = int(a["N_CTX"])
     _covers("attention_lse_kernel grid[0]*BLOCK_M", grid[0] * int(a["BLOCK_M"]), s)

@@ -328,6 +328,50 @@ def test_numpy_arguments_are_written_back_and_async_numpy_defers(oracle):
     assert ops.softmax_kernel.last_launch["h2d_bytes"] == x.nbytes  # the dense output is not copied in
 
 
+def test_piecewise_staging_of_numpy_arguments_gives_the_single_piece_result(monkeypatch):
+    """Large NumPy launches are staged, run and copied back piece by piece on side streams.  The pieces are
+    independent rows / elements / M-blocks / (batch, head) slices, so the result must be bit-identical to
+    the one-piece launch on device tensors; thresholds are lowered so that small arrays take the path."""
+    from enceladus_b200.runtime import jit
+
+    monkeypatch.setattr(jit, "PIPELINE_MIN_BYTES", 1)
+    monkeypatch.setattr(jit, "PIPELINE_PIECE_BYTES", 64 << 10)
+    r = np.random.default_rng(21)
+
+    def same(kernel, got, want, pieces_at_least=2):
+        got, want = (got if isinstance(got, tuple) else (got,)), (want if isinstance(want, tuple) else (want,))
+        assert kernel.last_launch.get("pieces", 0) >= pieces_at_least, kernel.last_launch
+        for g, w in zip(got, want):
+            assert isinstance(g, np.ndarray)
+            np.testing.assert_array_equal(g.view(np.uint8), host(w).view(np.uint8))
+
+    x = randn(r, (1000, 520), F32)                       # ragged row count, rows not a multiple of 256 bytes
+    same(ops.softmax_kernel, ops.softmax(x), ops.softmax(torch_of(x)))
+    xb, w, b = randn(r, (777, 1024), BF16), randn(r, (1024,), BF16), randn(r, (1024,), BF16)
+    same(ops.layernorm_kernel, ops.layernorm(xb, w, b), ops.layernorm(torch_of(xb), torch_of(w), torch_of(b)))
+    same(ops.rmsnorm_kernel, ops.rmsnorm(xb, w), ops.rmsnorm(torch_of(xb), torch_of(w)))
+    v = randn(r, (300001,), F32)
+    same(ops.tanh_gelu_kernel, ops.tanh_gelu(v), ops.tanh_gelu(torch_of(v)))
+    xg, bg = randn(r, (900, 200), F16), randn(r, (200,), F16)
+    same(ops.fused_gelu_kernel, ops.fused_gelu(xg, bg, 0.5), ops.fused_gelu(torch_of(xg), torch_of(bg), 0.5))
+    same(ops.add_kernel, ops.add(v, v[::-1].copy()), ops.add(torch_of(v), torch_of(v[::-1].copy())))
+    a, bm, bias = randn(r, (600, 256), F16), randn(r, (256, 512), F16), randn(r, (512,), F16)
+    same(ops.matmul_bias_gelu_kernel, ops.matmul_bias_gelu(a, bm, bias), ops.matmul_bias_gelu(torch_of(a), torch_of(bm), torch_of(bias)))
+    q, k, vv = (randn(r, (2, 3, 256, 64), F16) for _ in range(3))  # lse rows of 1 KB keep every piece 256-byte aligned
+    same(ops.attention_lse_kernel, ops.attention(q, k, vv, True, return_lse=True),
+         ops.attention(torch_of(q), torch_of(k), torch_of(vv), True, return_lse=True))
+    # an array whose flat view is not a view (strided rows) takes the one-piece path
+    xs = randn(r, (512, 1024), F32)[:, :512]
+    got = ops.softmax(xs)
+    assert "pieces" not in ops.softmax_kernel.last_launch
+    np.testing.assert_array_equal(got, host(ops.softmax(torch_of(np.ascontiguousarray(xs)))))
+    # ... and so does a strided NumPy output, whose gaps between rows must stay untouched
+    full = np.full((9, 2048), 7.0, np.float32)
+    ops.softmax_kernel[(9,)](full[:, :1000], xs[2:11, 4:504], 1024, 2048, 500, BLOCK=512)
+    np.testing.assert_array_equal(full[:, :500], host(ops.softmax(torch_of(np.ascontiguousarray(xs[2:11, 4:504])))))
+    assert full[:, 500:].min() == 7.0 and full[:, 500:].max() == 7.0
+
+
 def test_injected_failure_surfaces_as_cuda_error():
     x = torch_of(np.zeros((2, 8), np.float32))
     N.load().enc_test_fail_next(N.ERR_LAUNCH)
