@@ -158,9 +158,18 @@ def workloads(scale: float = 1.0):
             bias = (0.1 * torch.randn(n, device="cuda", generator=g)).half()
             return a, b, bias, torch.empty(m, n, device="cuda", dtype=torch.float16)
 
-        return dict(name=f"matmul_bias_gelu_f16_{m}x{n}x{k}", kernel="matmul", unit="TFLOP/s", bound="tensor",
+        def host():
+            r = np.random.default_rng(0)
+            sc = np.float32(1 / math.sqrt(k))
+            return ((r.random((m, k), dtype=np.float32) * 2 - 1) * sc).astype(np.float16), \
+                   ((r.random((k, n), dtype=np.float32) * 2 - 1) * sc).astype(np.float16), \
+                   (0.1 * r.standard_normal(n, dtype=np.float32)).astype(np.float16)
+
+        return dict(name=f"matmul_bias_gelu_f16_{m}x{n}x{k}", kernel="matmul", jit=ops.matmul_bias_gelu_kernel,
+                    unit="TFLOP/s", bound="tensor",
                     dtype="f16", work=2 * m * n * k, set_bytes=(m * k + k * n + m * n) * 2, make=make,
-                    run=lambda s: ops.matmul_bias_gelu(s[0], s[1], s[2], s[3]))
+                    run=lambda s: ops.matmul_bias_gelu(s[0], s[1], s[2], s[3]),
+                    host=host, run_host=lambda h: ops.matmul_bias_gelu(h[0], h[1], h[2]))
 
     # ---- config 4: attention bf16 [8, 32, 4096, 128] ----
     def attention_wl(causal):
@@ -172,9 +181,17 @@ def workloads(scale: float = 1.0):
             return q, k, v, torch.empty_like(q), torch.empty(z, h, s_, device="cuda")
 
         flops = 4 * z * h * s_ * s_ * d // (2 if causal else 1)
+        zh = 2  # batches of the host (end-to-end) leg: a quarter of the workload, to bound the bench's run time
+
+        def host():
+            r = np.random.default_rng(0)
+            return tuple(_bf16_host((zh, h, s_, d), r) for _ in range(3))
+
         return dict(name=f"attention_bf16_8x32x4096x128_{'causal' if causal else 'full'}", kernel="attention",
+                    jit=ops.attention_kernel,
                     unit="TFLOP/s", bound="tensor", dtype="bf16", work=flops, set_bytes=4 * z * h * s_ * d * 2,
-                    make=make, run=lambda s: ops.attention(s[0], s[1], s[2], causal, None, s[3]))
+                    make=make, run=lambda s: ops.attention(s[0], s[1], s[2], causal, None, s[3]),
+                    host=host, run_host=lambda hh: ops.attention(hh[0], hh[1], hh[2], causal), host_units=flops * zh // z)
 
     # ---- config 5: histogram / cumsum ----
     def hist_wl(kind):
@@ -518,7 +535,7 @@ def reference_arm(args) -> None:
             samples.append(info["value"])
     value = float(np.mean(samples))
     rows_bytes = 2 * m * n * 2
-    line = {"impl": "reference", "metric": "LayerNorm bf16 [16384,4096] algorithmic HBM GB/s (read+write)",
+    line = {"impl": "reference", "metric": "layernorm_bf16_16384x4096 algorithmic HBM GB/s (read+write)",
             "value": value, "unit": "GB/s", "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": rows_bytes / (value * 1e9) * 1e3, "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
