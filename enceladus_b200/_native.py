@@ -21,7 +21,7 @@ OK, ERR_BAD_ARG, ERR_UNSUPPORTED, ERR_LAUNCH, ERR_DEVICE_WAIT, ERR_NO_MEMORY = r
 # enc_dtype
 F32, F16, BF16, I32, I8, I16, I64, U8 = range(8)
 # enc_kernel
-K_SOFTMAX, K_LAYERNORM, K_RMSNORM, K_GELU, K_MATMUL, K_ATTENTION, K_HISTOGRAM, K_CUMSUM, K_ADD = range(9)
+K_SOFTMAX, K_LAYERNORM, K_RMSNORM, K_GELU, K_MATMUL, K_ATTENTION, K_HISTOGRAM, K_CUMSUM, K_ADD, K_MATMUL_INT = range(10)
 VARIANT_AUTO = -1
 
 
@@ -63,6 +63,7 @@ SIGNATURES: dict[str, list] = {
     "enc_cumsum_out_dtype": [_i],
     "enc_sum": [_p, _p, _i64, _i, _p],
     "enc_matmul": [_p, _p, _p, _p, _i64, _i64, _i64, _i64, _i64, _i64, _i, _i, _i, _p],
+    "enc_matmul_int": [_p, _p, _p, _i64, _i64, _i64, _i64, _i64, _i64, _i, _i, _p],
     "enc_attention_fwd": [_p, _p, _p, _p, _p, _i64, _i64, _i64, _i64, _i64, _f, _i, _i, _i, _p],
     "enc_test_fail_next": [_i],
     "enc_test_device_wait": [C.c_uint, _p],

@@ -18,6 +18,8 @@ int matmul_variants();
 void matmul_variant_info(int v, char *out, size_t n);
 int attention_variants();
 void attention_variant_info(int v, char *out, size_t n);
+int int_matmul_variants();
+void int_matmul_variant_info(int v, char *out, size_t n);
 
 namespace {
 thread_local char g_error[1024] = "";
@@ -83,7 +85,7 @@ unsigned int *device_error_word() {
     return g_error_word[dev];
 }
 
-bool make_tensor_map(CUtensorMap *map, const void *base, int elem_is_bf16, int rank, const uint64_t *dims,
+bool make_tensor_map(CUtensorMap *map, const void *base, int elem, int rank, const uint64_t *dims,
                      const uint64_t *strides_bytes, const uint32_t *box, char *err, size_t errlen) {
     using EncodeFn = CUresult (*)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
                                   const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
@@ -107,7 +109,9 @@ bool make_tensor_map(CUtensorMap *map, const void *base, int elem_is_bf16, int r
         e[i] = 1;
         if (i + 1 < rank) s[i] = strides_bytes[i];
     }
-    const CUresult r = encode(map, elem_is_bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16,
+    const CUtensorMapDataType dt = elem == TMAP_U8 ? CU_TENSOR_MAP_DATA_TYPE_UINT8
+                                   : elem == TMAP_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+    const CUresult r = encode(map, dt,
                               (cuuint32_t)rank, const_cast<void *>(base), d, s, b, e, CU_TENSOR_MAP_INTERLEAVE_NONE,
                               CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
@@ -178,6 +182,7 @@ extern "C" int enc_num_variants(int kernel) {
         case ENC_K_CUMSUM: return enc::scan_variants();
         case ENC_K_MATMUL: return enc::matmul_variants();
         case ENC_K_ATTENTION: return enc::attention_variants();
+        case ENC_K_MATMUL_INT: return enc::int_matmul_variants();
         case ENC_K_ADD: return 1;
         default: return 0;
     }
@@ -194,6 +199,7 @@ extern "C" int enc_variant_info(int kernel, int variant, char *out, size_t n) {
         case ENC_K_CUMSUM: enc::scan_variant_info(variant, out, n); break;
         case ENC_K_MATMUL: enc::matmul_variant_info(variant, out, n); break;
         case ENC_K_ATTENTION: enc::attention_variant_info(variant, out, n); break;
+        case ENC_K_MATMUL_INT: enc::int_matmul_variant_info(variant, out, n); break;
         default: snprintf(out, n, "cta_threads=256 grid-stride"); break;
     }
     return ENC_OK;

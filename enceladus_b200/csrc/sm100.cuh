@@ -200,7 +200,8 @@ __host__ __device__ constexpr uint32_t idesc_f16(int fmt, bool b_mn_major, int m
 
 // Host side: builds a 2-D/3-D tiled tensor map with 128-byte swizzle and zero fill out of bounds.
 // dims/strides innermost first; strides[0] is implied by the element size.  Returns false on failure.
-bool make_tensor_map(CUtensorMap *map, const void *base, int elem_is_bf16, int rank, const uint64_t *dims,
+enum { TMAP_F16 = 0, TMAP_BF16 = 1, TMAP_U8 = 2 };  // element type of a tensor map (8-bit integers of either sign: TMAP_U8)
+bool make_tensor_map(CUtensorMap *map, const void *base, int elem, int rank, const uint64_t *dims,
                      const uint64_t *strides_bytes, const uint32_t *box, char *err, size_t errlen);
 
 }  // namespace enc

@@ -166,6 +166,22 @@ def matmul_tuned(a, b, c=None):
     return c
 
 
+# ---- integer matmul (benchmarks/bench_matmul.py:100-131) ------------------------------------------
+@enceladus.jit
+def int8_matmul_kernel(a_ptr, b_ptr, c_ptr, M, N, K, BM: tl.constexpr, BN: tl.constexpr, BK: tl.constexpr):
+    """C[int32] = A @ B for dense row-major integer A [M, K] and B [K, N]: int32 accumulation, exact, products
+    and sums wrap modulo 2^32 (an integer `tl.dot` per K block)."""
+
+
+def int_matmul(a, b, c=None, bm: int = 128, bn: int = 256, bk: int = 128):
+    """Returns the exact int32 product of two contiguous integer matrices (int8, uint8, int16 or int32)."""
+    (m, k), (_, n) = a.shape, b.shape
+    if c is None:
+        c = enceladus.new_empty(a, (m, n), np.int32)
+    int8_matmul_kernel[(enceladus.cdiv(n, bn), enceladus.cdiv(m, bm))](a, b, c, m, n, k, BM=bm, BN=bn, BK=bk)
+    return c
+
+
 # ---- 08 flash attention ------------------------------------------------------------------------
 @enceladus.jit
 def attention_kernel(q_ptr, k_ptr, v_ptr, o_ptr, sm_scale, N_CTX, stride_h, stride_m, HEAD_DIM: tl.constexpr,

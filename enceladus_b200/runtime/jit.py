@@ -252,7 +252,8 @@ class CompiledKernel:
 
 _ENTRY_POINTS = {N.K_SOFTMAX: "enc_softmax", N.K_LAYERNORM: "enc_layernorm", N.K_RMSNORM: "enc_rmsnorm",
                  N.K_GELU: "enc_gelu", N.K_MATMUL: "enc_matmul", N.K_ATTENTION: "enc_attention_fwd",
-                 N.K_HISTOGRAM: "enc_histogram", N.K_CUMSUM: "enc_cumsum", N.K_ADD: "enc_add"}
+                 N.K_HISTOGRAM: "enc_histogram", N.K_CUMSUM: "enc_cumsum", N.K_ADD: "enc_add",
+                 N.K_MATMUL_INT: "enc_matmul_int"}
 
 
 def launch(ad, bound: dict[str, Any], grid: tuple[int, int, int], variant: int, jf: JITFunction | None) -> None:

@@ -264,6 +264,23 @@ def _matmul_ptr(a, grid, variant, stream):
     _matmul_common(a, grid, variant, stream, bias=False, epilogue=0)
 
 
+# ---- int8_matmul_kernel(a, b, c, M, N, K, BM, BN, BK): dense row-major integer operands, int32 result -------
+@register("int8_matmul_kernel", "a_ptr b_ptr c_ptr M N K BM BN BK", "a_ptr b_ptr c_ptr", "c_ptr", N.K_MATMUL_INT,
+          extents=lambda a, g: {"c_ptr": int(a["M"]) * int(a["N"])},
+          split=lambda a, g: Split(int(a["M"]), {"a_ptr": int(a["K"]), "c_ptr": int(a["N"])},
+                                   lambda n: (g[0], -(-n // int(a["BM"])), 1), lambda n: {"M": n}))
+def _int_matmul(a, grid, variant, stream):
+    m, n, k = int(a["M"]), int(a["N"]), int(a["K"])
+    _covers("int8_matmul_kernel grid[0]*BN", grid[0] * int(a["BN"]), n)
+    _covers("int8_matmul_kernel grid[1]*BM", grid[1] * int(a["BM"]), m)
+    dt = _same_dtype(a, "a_ptr", "b_ptr")
+    if dt not in (N.I8, N.U8, N.I16, N.I32):
+        raise TypeError(f"int8_matmul_kernel takes int8, uint8, int16 or int32 operands, not {interop.element_dtype(a['a_ptr'])}")
+    if _code(a["c_ptr"]) != N.I32:
+        raise TypeError("argument `c_ptr` must be int32")
+    N.call("enc_matmul_int", _ptr(a["a_ptr"]), _ptr(a["b_ptr"]), _ptr(a["c_ptr"]), m, n, k, k, n, n, dt, variant, stream)
+
+
 # ---- attention_kernel(q, k, v, o, sm_scale, N_CTX, stride_h, stride_m, HEAD_DIM, BLOCK_M, BLOCK_N, CAUSAL)
 @register("attention_kernel",
           "q_ptr k_ptr v_ptr o_ptr sm_scale N_CTX stride_h stride_m HEAD_DIM BLOCK_M BLOCK_N CAUSAL",

@@ -62,7 +62,8 @@ typedef enum {
     ENC_K_HISTOGRAM = 6,
     ENC_K_CUMSUM = 7,
     ENC_K_ADD = 8,
-    ENC_K_COUNT = 9
+    ENC_K_MATMUL_INT = 9,
+    ENC_K_COUNT = 10
 } enc_kernel;
 
 #define ENC_VARIANT_AUTO (-1)
@@ -184,6 +185,16 @@ int enc_sum(const void *in, void *total, int64_t n, int dtype, void *stream);
 int enc_matmul(const void *a, const void *b, const void *bias, void *c, int64_t M, int64_t N,
                int64_t K, int64_t lda, int64_t ldb, int64_t ldc, int epilogue, int dtype,
                int variant, void *stream);
+
+/* C = A @ B for integer operands: A [M,K] (lda), B [K,N] (ldb), both of `dtype`, C [M,N] int32 (ldc), row-major
+ * with unit inner stride.  int32 accumulation, exact: products and sums wrap modulo 2^32
+ * (integer tl.dot, src/enceladus/language/ops.py:1255-1259).  ENC_I8 and ENC_U8 run on the tcgen05 tensor cores
+ * (kind::i8) when A and B are 16-byte aligned with leading dimensions that are multiples of 16, otherwise and for
+ * ENC_I16 / ENC_I32 on CUDA cores.  Out-of-range tile elements read as zero and are not stored.
+ * Replaces int8_matmul_kernel[(cdiv(N,BN),cdiv(M,BM))](a, b, c, M, N, K, BM, BN, BK)   benchmarks/bench_matmul.py:100-131
+ * and the integer tl.dot kernels of                                                   tests/test_interpreter.py:808-835 */
+int enc_matmul_int(const void *a, const void *b, void *c, int64_t M, int64_t N, int64_t K, int64_t lda, int64_t ldb,
+                   int64_t ldc, int dtype, int variant, void *stream);
 
 /* Flash-attention forward over `bh` independent (batch, head) slices of shape [seq, head_dim]:
  * O = softmax(Q K^T * sm_scale [causal]) V, base-2 online softmax in float32, P rounded to the input

@@ -185,6 +185,13 @@ def matmul_bias_gelu(a, b, bias, bk: int = 32) -> np.ndarray:
     return _store(y, a.dtype)
 
 
+def int_matmul(a, b) -> np.ndarray:
+    """Integer `tl.dot`: int32 accumulation, exact, products and sums wrap modulo 2^32
+    (src/enceladus/language/ops.py:1255-1259; the reference's own check is
+    tests/test_interpreter.py:804-805: the int64 product cast to int32)."""
+    return (a.astype(np.int64) @ b.astype(np.int64)).astype(np.int32)
+
+
 # ---------------------------------------------------------------------------------------------
 # Flash-attention forward — examples/08_flash_attention.py:30-70
 # ---------------------------------------------------------------------------------------------

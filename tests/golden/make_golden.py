@@ -177,6 +177,43 @@ def main() -> None:
         g.put(k + "_a", aa), g.put(k + "_b", bb), g.put(k + "_c", m4.matmul_desc(aa, bb))
     np.savez_compressed(out / "matmul.npz", **g)
 
+    # ---- integer matmul: tests/test_interpreter.py:808-835 (shapes, dtypes, full-range values) ----
+    # The kernel below is written for this script (pointer loads with edge masks, one tl.dot per K block into
+    # an int32 accumulator) and executed by the reference interpreter.
+    @enceladus.jit
+    def int_dot_kernel(a_ptr, b_ptr, c_ptr, M, N, K, BM: tl.constexpr, BN: tl.constexpr, BK: tl.constexpr):
+        rm = tl.program_id(1) * BM + tl.arange(0, BM)
+        rn = tl.program_id(0) * BN + tl.arange(0, BN)
+        acc = tl.zeros((BM, BN), dtype=tl.int32)
+        for k0 in range(0, K, BK):
+            rk = k0 + tl.arange(0, BK)
+            at = tl.load(a_ptr + rm[:, None] * K + rk[None, :], mask=(rm[:, None] < M) & (rk[None, :] < K), other=0)
+            bt = tl.load(b_ptr + rk[:, None] * N + rn[None, :], mask=(rk[:, None] < K) & (rn[None, :] < N), other=0)
+            acc = tl.dot(at, bt, acc)
+        tl.store(c_ptr + rm[:, None] * N + rn[None, :], acc, mask=(rm[:, None] < M) & (rn[None, :] < N))
+
+    g = Bag()
+    r5 = np.random.default_rng(11)
+    for dt in (np.int8, np.uint8, np.int16, np.int32):
+        for (mm, kk_, nn) in ((64, 64, 64), (50, 100, 33)):
+            info = np.iinfo(dt)
+            aa = r5.integers(info.min, info.max, (mm, kk_), dt, endpoint=True)
+            bb = r5.integers(info.min, info.max, (kk_, nn), dt, endpoint=True)
+            cc = np.zeros((mm, nn), np.int32)
+            int_dot_kernel[(enceladus.cdiv(nn, 32), enceladus.cdiv(mm, 32))](aa, bb, cc, mm, nn, kk_, BM=32, BN=32, BK=32)
+            key = f"{np.dtype(dt).name}_{mm}x{kk_}x{nn}"
+            g.put(key + "_a", aa), g.put(key + "_b", bb), g.put(key + "_c", cc)
+    # every sum exceeds 2^24 and is odd: float32 accumulation would round it (test_interpreter.py:822-835)
+    for dt, kk_ in ((np.int8, 2048), (np.uint8, 512)):
+        ext = np.iinfo(dt).min if dt == np.int8 else np.iinfo(dt).max
+        aa, bb = np.full((8, kk_), ext, dt), np.full((kk_, 8), ext, dt)
+        aa[:, 0] = 1
+        cc = np.zeros((8, 8), np.int32)
+        int_dot_kernel[(1, 1)](aa, bb, cc, 8, 8, kk_, BM=8, BN=8, BK=32)
+        key = f"exact_{np.dtype(dt).name}_{kk_}"
+        g.put(key + "_a", aa), g.put(key + "_b", bb), g.put(key + "_c", cc)
+    np.savez_compressed(out / "int_matmul.npz", **g)
+
     # ---- attention: tests/test_attention.py:20-49 (inputs are regenerated from the seed) ----
     g = Bag()
     m = ex("08_flash_attention")

@@ -100,3 +100,49 @@ def test_autotuned_matmul_picks_a_variant(oracle, tmp_path, monkeypatch):
     got = host(ops.matmul_tuned(torch_of(a), torch_of(b)))
     assert_close(got, oracle.matmul(a, b, 64))
     assert list(tmp_path.rglob("*.json")), "the tuning result was not persisted"
+
+
+# ---- integer matmul: exact, int32 accumulation that wraps modulo 2^32 ------------------------------------
+def test_int_matmul_golden():
+    g = load_golden("int_matmul")
+    keys = [k[:-2] for k in g if k.endswith("_a")]
+    assert len(keys) == 10
+    for k in keys:
+        a, b = g[k + "_a"], g[k + "_b"]
+        for dev in (False, True):  # NumPy arguments and device tensors
+            got = ops.int_matmul(torch_of(a), torch_of(b)) if dev else ops.int_matmul(a, b)
+            np.testing.assert_array_equal(host(got), g[k + "_c"], err_msg=k)
+
+
+@pytest.mark.parametrize("dt", [np.int8, np.uint8])
+@pytest.mark.parametrize("mkn", [(512, 1024, 768), (300, 2000, 130), (128, 4096, 256), (1000, 144, 1040)])
+def test_int8_matmul_on_tensor_cores_is_exact(oracle, dt, mkn):
+    """Full-range 8-bit operands on the tcgen05 path (K and N multiples of 16), every tile variant, ragged edges."""
+    m, k, n = mkn
+    r = np.random.default_rng(m + k + n)
+    info = np.iinfo(dt)
+    a = r.integers(info.min, info.max, (m, k), dt, endpoint=True)
+    b = r.integers(info.min, info.max, (k, n), dt, endpoint=True)
+    want = oracle.int_matmul(a, b)
+    at, bt = torch_of(a), torch_of(b)
+    for variant in range(N.num_variants(N.K_MATMUL_INT)):
+        c = enceladus.new_empty(at, (m, n), np.int32)
+        ops.int8_matmul_kernel[(enceladus.cdiv(n, 128), enceladus.cdiv(m, 128))](at, bt, c, m, n, k, BM=128, BN=128, BK=128,
+                                                                           variant=variant)
+        np.testing.assert_array_equal(host(c), want, err_msg=f"variant {variant}")
+
+
+def test_int_matmul_wraps_and_takes_unaligned_and_wide_types(oracle):
+    r = np.random.default_rng(5)
+    # sums beyond 2^31: int8 extremes over K = 2^17 wrap modulo 2^32 on the tensor-core path
+    k = 1 << 17
+    a, b = np.full((128, k), -128, np.int8), np.full((k, 16), -128, np.int8)
+    np.testing.assert_array_equal(host(ops.int_matmul(torch_of(a), torch_of(b))), oracle.int_matmul(a, b))
+    # shapes TMA cannot describe (odd leading dimensions) and 16/32-bit operands: CUDA cores, same result
+    for dt, (m, kk, n) in ((np.int8, (50, 100, 33)), (np.uint8, (77, 45, 130)), (np.int16, (64, 200, 96)), (np.int32, (33, 70, 65))):
+        info = np.iinfo(dt)
+        a = r.integers(info.min, info.max, (m, kk), dt, endpoint=True)
+        b = r.integers(info.min, info.max, (kk, n), dt, endpoint=True)
+        np.testing.assert_array_equal(host(ops.int_matmul(torch_of(a), torch_of(b))), oracle.int_matmul(a, b), err_msg=str(dt))
+    with pytest.raises(TypeError, match="int8, uint8, int16 or int32"):
+        ops.int_matmul(torch_of(np.zeros((8, 8), np.float16)), torch_of(np.zeros((8, 8), np.float16)))

@@ -68,6 +68,15 @@ def test_matmul(oracle):
             same(got, g[k + "_c"])
 
 
+def test_int_matmul(oracle):
+    """Integer tl.dot: int8, uint8, int16, int32 at full range (wraps modulo 2^32) and the sums float32 cannot hold."""
+    g = load_golden("int_matmul")
+    keys = [k[:-2] for k in g if k.endswith("_a")]
+    assert len(keys) == 10
+    for k in keys:
+        same(oracle.int_matmul(g[k + "_a"], g[k + "_b"]), g[k + "_c"])
+
+
 def attention_cases():
     g = load_golden("attention")
     i = 0
