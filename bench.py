@@ -171,6 +171,18 @@ def workloads(scale: float = 1.0):
                     run=lambda s: ops.matmul_bias_gelu(s[0], s[1], s[2], s[3]),
                     host=host, run_host=lambda h: ops.matmul_bias_gelu(h[0], h[1], h[2]))
 
+    # ---- not a graded config: the reference's exact int8 matmul (benchmarks/bench_matmul.py:100-131) ----
+    def int8_matmul_wl(m, n, k):
+        def make(i):
+            g = gen(i)
+            return (torch.randint(-128, 128, (m, k), device="cuda", dtype=torch.int8, generator=g),
+                    torch.randint(-128, 128, (k, n), device="cuda", dtype=torch.int8, generator=g),
+                    torch.empty(m, n, device="cuda", dtype=torch.int32))
+
+        return dict(name=f"matmul_int8_{m}x{n}x{k}", kernel="matmul_int", jit=ops.int8_matmul_kernel, unit="TOP/s",
+                    bound="tensor", peak_scale=2.0, dtype="s8", work=2 * m * n * k, set_bytes=m * k + k * n + 4 * m * n, make=make,
+                    run=lambda s: ops.int_matmul(s[0], s[1], s[2]))
+
     # ---- config 4: attention bf16 [8, 32, 4096, 128] ----
     def attention_wl(causal):
         z, h, s_, d = 8, 32, 4096, 128
@@ -269,6 +281,7 @@ def workloads(scale: float = 1.0):
     if N.num_variants(N.K_MATMUL) > 0:
         W["matmul_8192"] = lambda: matmul_wl(8192, 8192, 8192)
         W["matmul_4096x4096x16384"] = lambda: matmul_wl(4096, 4096, 16384)
+        W["matmul_int8_8192"] = lambda: int8_matmul_wl(8192, 8192, 8192)
     if N.num_variants(N.K_ATTENTION) > 0:
         W["attention_full"] = lambda: attention_wl(False)
         W["attention_causal"] = lambda: attention_wl(True)
@@ -437,7 +450,9 @@ def bench_workload(wl: dict, steps: int, warmup: int, pk: dict, pk_kind: str, sa
     ms = timed_region(wl["run"], sets, steps, warmup, graph)
     m1 = sampler.mark() if sampler else 0
     achieved = wl["work"] / (ms * 1e-3) / (1e9 if wl["unit"] == "GB/s" else 1e12)
-    peak = pk["hbm_gbs"] if wl["bound"] == "hbm" else pk["bf16_tflops"]
+    peak = pk["hbm_gbs"] if wl["bound"] == "hbm" else pk["bf16_tflops"] * wl.get("peak_scale", 1.0)
+    if "peak_scale" in wl:  # no int8 GEMM was measured on this pool: the 8-bit rate of the tensor cores is twice the 16-bit one
+        pk_kind = f"{wl['peak_scale']:g} x {pk_kind} bf16"
     row = {
         "name": wl["name"], "value": achieved * WORLD, "unit": wl["unit"], "ms_per_step": ms, "steps": steps,
         "warmup": warmup, "dtype": wl["dtype"], "buffer_sets": nsets, "cuda_graph": graph,
@@ -477,6 +492,83 @@ def bench_workload(wl: dict, steps: int, warmup: int, pk: dict, pk_kind: str, sa
         if cpu and RANK == 0:
             row["cpu_baseline"] = cpu_baseline(wl, h, threads=1)
     return row
+
+
+def reference_shape_rows(pk: dict) -> list[dict]:
+    """The shapes of the reference's own benchmark reports, so that its published numbers (Apple M4 Pro, Metal;
+    benchmarks/results/2026-09-27-applegpu_g16s-2.md) have like-for-like rows.  Device-resident inputs, same
+    timing as every other row; not graded configurations and no roofline claim beyond the fraction."""
+    import torch
+
+    from enceladus_b200 import ops
+
+    dev = "cuda"
+    g = torch.Generator(device=dev).manual_seed(1234 + RANK)
+    rows = []
+
+    def timed(name, unit, work, bound, make, run, published, nsets=None):
+        set_bytes = sum(t.numel() * t.element_size() for t in make())
+        nsets = nsets or max(2, min(16, -(-ROTATE_BYTES // max(set_bytes, 1))))
+        sets = [make() for _ in range(nsets)]
+        run(sets[0])
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        run(sets[-1])
+        e1.record()
+        torch.cuda.synchronize()
+        steps = max(10, min(200, int(1.0 / max(e0.elapsed_time(e1), 1e-3)) + 1))
+        ms = timed_region(run, sets, steps, 3, USE_GRAPH)
+        value = work / (ms * 1e-3) / (1e9 if unit == "GB/s" else 1e12)
+        peak = pk["hbm_gbs"] if bound == "hbm" else pk["bf16_tflops"] * (2.0 if unit == "TOP/s" else 1.0)
+        rows.append({"name": name, "value": value, "unit": unit, "ms_per_step": ms, "steps": steps, "frac_of_peak": value / peak,
+                     "published_m4pro": published, "vs_published": value / published if published else None})
+        del sets
+        torch.cuda.empty_cache()
+
+    def randn(*shape, dt=torch.float32):
+        return torch.randn(*shape, device=dev, generator=g).to(dt)
+
+    m = n = 4096
+    for dt, name, pub in ((torch.float32, "f32", 241.9), (torch.float16, "f16", 256.3)):
+        timed(f"softmax_{name}_4096x4096", "GB/s", 2 * m * n * dt.itemsize, "hbm", lambda: (randn(m, n, dt=dt) * 4, torch.empty(m, n, device=dev, dtype=dt)),
+              lambda s: ops.softmax_kernel[(m,)](s[1], s[0], n, n, n, BLOCK=n), pub)
+    for dt, name, pl, pr in ((torch.float32, "f32", 237.4, 239.5), (torch.float16, "f16", 241.9, 247.4)):
+        mk = lambda: (randn(m, n, dt=dt), randn(n, dt=dt), randn(n, dt=dt), torch.empty(m, n, device=dev, dtype=dt),  # noqa: E731
+                      torch.empty(m, device=dev), torch.empty(m, device=dev))
+        timed(f"layernorm_{name}_4096x4096", "GB/s", 2 * m * n * dt.itemsize, "hbm", mk,
+              lambda s: ops.layernorm_kernel[(m,)](s[0], s[3], s[1], s[2], s[4], s[5], n, n, n, 1e-5, BLOCK=n), pl)
+        timed(f"rmsnorm_{name}_4096x4096", "GB/s", 2 * m * n * dt.itemsize, "hbm", mk,
+              lambda s: ops.rmsnorm_kernel[(m,)](s[0], s[1], s[3], n, n, n, 1e-6, BLOCK=n), pr)
+    na = 1 << 26
+    timed("vector_add_f32_2p26", "GB/s", 3 * na * 4, "hbm", lambda: (randn(na), randn(na), torch.empty(na, device=dev)),
+          lambda s: ops.add_kernel[(na // 1024,)](s[0], s[1], s[2], na, BLOCK=1024), 236.6)
+    timed("row_cumsum_f32_4096x4096", "GB/s", 2 * m * n * 4, "hbm", lambda: (randn(m, n), torch.empty(m, n, device=dev)),
+          lambda s: ops.cumsum_kernel[(m,)](s[1], s[0], m, n, n, n, REVERSE=False, BLOCK_M=1, BLOCK_N=n), 242.2)
+    nh = 1 << 24
+    for bins, pub in ((64, 31.1), (4096, 62.5)):
+        timed(f"histogram_f32_2p24_{bins}bins", "GB/s", nh * 4, "hbm", lambda: (torch.rand(nh, device=dev, generator=g), torch.zeros(bins, device=dev, dtype=torch.int32)),
+              lambda s: ops.histogram_kernel[(nh // 1024,)](s[0], s[1], nh, 0.0, float(bins), NUM_BINS=bins, BLOCK=1024), pub)
+    for (mm, nn, kk), pub in (((4096, 4096, 4096), 6.04), ((2000, 2000, 2000), 5.86), ((513, 513, 513), 4.31), ((1024, 4096, 1024), 6.03)):
+        mk = lambda: (randn(mm, kk, dt=torch.float16) / math.sqrt(kk), randn(kk, nn, dt=torch.float16), randn(nn, dt=torch.float16) * 0.1,  # noqa: E731
+                      torch.empty(mm, nn, device=dev, dtype=torch.float16))
+        timed(f"matmul_f16_{mm}x{nn}x{kk}", "TFLOP/s", 2 * mm * nn * kk, "tensor", mk, lambda s: ops.matmul_desc(s[0], s[1], s[3]), pub, nsets=4)
+        if mm == 4096:
+            timed("matmul_bias_gelu_f16_4096x4096x4096", "TFLOP/s", 2 * mm * nn * kk, "tensor", mk,
+                  lambda s: ops.matmul_bias_gelu(s[0], s[1], s[2], s[3]), 6.00, nsets=4)
+    timed("matmul_int8_4096x4096x4096", "TOP/s", 2 * 4096**3, "tensor",
+          lambda: (torch.randint(-128, 128, (4096, 4096), device=dev, dtype=torch.int8, generator=g),
+                   torch.randint(-128, 128, (4096, 4096), device=dev, dtype=torch.int8, generator=g),
+                   torch.empty(4096, 4096, device=dev, dtype=torch.int32)),
+          lambda s: ops.int_matmul(s[0], s[1], s[2]), 4.75, nsets=4)
+    for (seq, d), (pn, pc) in (((4096, 128), (5.04, 4.93)), ((4096, 64), (5.26, 5.06)), ((2048, 128), (5.23, None)), ((2048, 64), (4.83, None))):
+        mk = lambda: (*(randn(1, 16, seq, d, dt=torch.float16) for _ in range(3)), torch.empty(1, 16, seq, d, device=dev, dtype=torch.float16))  # noqa: E731
+        for causal, pub in ((False, pn), (True, pc)):
+            if pub is None and causal:
+                continue
+            timed(f"attention_f16_1x16x{seq}x{d}_{'causal' if causal else 'full'}", "TFLOP/s", 4 * 16 * seq * seq * d // (2 if causal else 1), "tensor",
+                  mk, lambda s: ops.attention(s[0], s[1], s[2], causal, None, s[3]), pub, nsets=8)
+    return rows
 
 
 def cpu_baseline(wl: dict, h, threads: int, budget_s: float = 20.0) -> dict:
@@ -558,6 +650,7 @@ def main() -> None:
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-graph", action="store_true", help="launch the timed steps eagerly instead of as one CUDA graph")
     ap.add_argument("--cpu-baseline-all", action="store_true")
+    ap.add_argument("--no-reference-shapes", action="store_true", help="skip the rows at the reference's own benchmark shapes")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
     global USE_GRAPH
@@ -599,6 +692,12 @@ def main() -> None:
                 launches += rows[-1]["steps"]
             except Exception as e:  # noqa: BLE001 - one failing workload must not hide the others
                 rows.append({"name": k, "error": f"{type(e).__name__}: {e}"})
+    ref_rows = []
+    if args.kernels == "all" and not args.no_reference_shapes:
+        try:
+            ref_rows = reference_shape_rows(pk)
+        except Exception as e:  # noqa: BLE001 - extra rows must not hide the graded ones
+            ref_rows = [{"error": f"{type(e).__name__}: {e}"}]
     if sampler:
         sampler.stop()
     if WORLD > 1:
@@ -617,6 +716,7 @@ def main() -> None:
                    "timed_region": "K launches captured in one CUDA graph" if head.get("cuda_graph") else "K eager launches"},
         "roofline": head["roofline"], "clocks": head.get("clocks"), "gpu_launches": launches,
         "e2e": head.get("e2e"), "cpu_baseline": head.get("cpu_baseline"), "per_kernel": rows,
+        "reference_shapes": ref_rows,
     }
     print(json.dumps(line))
 

@@ -315,9 +315,32 @@ int launch_tc(const void *A, const void *B, const MatmulArgs &args, int64_t lda,
 
 template <typename T>
 int launch_matmul(const void *A, const void *B, MatmulArgs args, int64_t lda, int64_t ldb, int variant, cudaStream_t st) {
-    const bool tma_ok = aligned16(A) && aligned16(B) && lda % 8 == 0 && ldb % 8 == 0 && args.K >= 1 &&
-                        args.M < (1LL << 31) && args.N < (1LL << 31) && args.K < (1LL << 31);
-    if (!tma_ok) {
+    const bool fits = args.K >= 1 && args.M < (1LL << 31) && args.N < (1LL << 31) && args.K < (1LL << 31);
+    const bool tma_ok = fits && aligned16(A) && aligned16(B) && lda % 8 == 0 && ldb % 8 == 0;
+    void *scratch = nullptr;
+    if (!tma_ok && fits && sizeof(T) == 2) {
+        // Operands TMA cannot describe (odd leading dimensions such as 513, misaligned bases): copy A and B into
+        // stream-ordered scratch with 16-byte-aligned pitches and run the tensor-core kernel on the copies; the
+        // copies move (M + N) * K elements against the 2 * M * N * K flops of the product.  C is written in
+        // place (the epilogue falls back to scalar stores when its rows are not 16-byte aligned).
+        const int64_t pa = (args.K + 7) / 8 * 8, pb = (args.N + 7) / 8 * 8;
+        const size_t a_bytes = ((size_t)args.M * pa * 2 + 255) / 256 * 256, b_bytes = (size_t)args.K * pb * 2;
+        if (cudaMallocAsync(&scratch, a_bytes + b_bytes, st) == cudaSuccess) {
+            void *sa = scratch, *sb = static_cast<char *>(scratch) + a_bytes;
+            cudaError_t e = cudaMemcpy2DAsync(sa, (size_t)pa * 2, A, (size_t)lda * 2, (size_t)args.K * 2, (size_t)args.M, cudaMemcpyDeviceToDevice, st);
+            if (e == cudaSuccess)
+                e = cudaMemcpy2DAsync(sb, (size_t)pb * 2, B, (size_t)ldb * 2, (size_t)args.N * 2, (size_t)args.K, cudaMemcpyDeviceToDevice, st);
+            if (e != cudaSuccess) {
+                cudaFreeAsync(scratch, st);
+                return fail(ENC_ERR_LAUNCH, "enc_matmul: staging unaligned operands: %s", cudaGetErrorString(e));
+            }
+            A = sa, B = sb, lda = pa, ldb = pb;
+        } else {
+            cudaGetLastError();  // no scratch: the CUDA-core kernel below needs none
+            scratch = nullptr;
+        }
+    }
+    if (!tma_ok && !scratch) {
         dim3 grid((unsigned)cdiv(args.N, 64), (unsigned)cdiv(args.M, 64));
         if (grid.y > 65535) return fail(ENC_ERR_UNSUPPORTED, "enc_matmul: unaligned operands with more than 4M rows");
         matmul_simple_kernel<T><<<grid, 256, 0, st>>>((const T *)A, (const T *)B, (const T *)args.bias, (T *)args.c, args.M,
@@ -326,13 +349,21 @@ int launch_matmul(const void *A, const void *B, MatmulArgs args, int64_t lda, in
     }
     args.error = device_error_word();
     if (!args.error) return fail(ENC_ERR_NO_MEMORY, "enc_matmul: cannot allocate the device status word");
-    if (variant < 0) variant = args.N <= 64 ? 3 : (args.N <= 128 ? 1 : 0);
-    switch (variant) {
-        case 0: return launch_tc<T, 256, 4>(A, B, args, lda, ldb, st);
-        case 1: return launch_tc<T, 128, 6>(A, B, args, lda, ldb, st);
-        case 2: return launch_tc<T, 256, 3>(A, B, args, lda, ldb, st);
-        default: return launch_tc<T, 64, 8>(A, B, args, lda, ldb, st);
+    if (variant < 0) {
+        // the widest tile that still gives most SMs a tile of their own
+        const int64_t sms = device_props().sm_count, mb = cdiv(args.M, BM);
+        variant = args.N <= 64 ? 3 : (args.N <= 128 ? 1 : 0);
+        if (variant == 0 && mb * cdiv(args.N, 256) * 10 < sms * 6) variant = mb * cdiv(args.N, 128) * 10 >= sms * 6 ? 1 : 3;
     }
+    int rc;
+    switch (variant) {
+        case 0: rc = launch_tc<T, 256, 4>(A, B, args, lda, ldb, st); break;
+        case 1: rc = launch_tc<T, 128, 6>(A, B, args, lda, ldb, st); break;
+        case 2: rc = launch_tc<T, 256, 3>(A, B, args, lda, ldb, st); break;
+        default: rc = launch_tc<T, 64, 8>(A, B, args, lda, ldb, st); break;
+    }
+    if (scratch) cudaFreeAsync(scratch, st);  // stream-ordered: freed after the kernel that reads it
+    return rc;
 }
 
 }  // namespace
