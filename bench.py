@@ -55,9 +55,10 @@ NCU_TRAFFIC: dict[str, float | None] = {
     "histogram_i32_2p30_zipf4096": 8 * 541_702_144,     # profiles/hist_zipf4096.md, captured at 2^27
     "cumsum_i32_2p30": 8 * 1_020_266_240,           # profiles/cumsum_i32.md, captured at 2^27
     "cumsum_f32_2p28": 2 * 1_020_002_560,           # profiles/cumsum_f32.md, captured at 2^27
-    "matmul_bias_gelu_f16_8192x8192x8192": 1_105_655_808,   # profiles/matmul.md
-    "attention_bf16_8x32x4096x128_full": 1_057_471_232,     # profiles/attention_full.md
-    "attention_bf16_8x32x4096x128_causal": 1_056_619_008,   # profiles/attention_causal.md
+    "matmul_bias_gelu_f16_8192x8192x8192": 1_109_306_624,   # profiles/matmul.md
+    "matmul_int8_8192x8192x8192": 571_891_712,              # profiles/matmul_int8.md
+    "attention_bf16_8x32x4096x128_full": 1_052_659_968,     # profiles/attention_full.md
+    "attention_bf16_8x32x4096x128_causal": 1_057_350_912,   # profiles/attention_causal.md
 }
 
 
