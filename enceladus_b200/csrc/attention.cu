@@ -793,6 +793,7 @@ attention_ts64_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
                 for (int b = 0; b < D / 64; ++b)
                     tma_load_3d(smem + L::Q_OFF + t * L::QTILE + b * (BM * 128), &tm_q, q_full, b * 64, (int)(m0 + t * BM), bh);
             bool ok = true;
+            PROF_T0();
             uint32_t ks = 0, kp = 0, vs = 0, vp = 0;  // ring positions
             for (int it = 0; it < 2 * nkv && ok; ++it) {  // K0, K1 V0, K2 V1, ..., V(n-1): the order of consumption
                 const bool is_v = it == 2 * nkv - 1 || (it != 0 && (it & 1) == 0);
@@ -801,12 +802,14 @@ attention_ts64_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
                 uint64_t *full = is_v ? &v_full[st] : &k_full[st];
                 ok = mbar_wait(is_v ? &v_empty[st] : &k_empty[st], ph ^ 1, abort);
                 if (!ok) break;
+                PROF_ADD(5);
                 uint8_t *dst = smem + (is_v ? L::V_OFF : L::K_OFF) + st * L::TILE;
                 mbar_expect_tx(full, L::TILE);
                 const CUtensorMap *tm = is_v ? &tm_v : &tm_k;
 #pragma unroll
                 for (int b = 0; b < D / 64; ++b) tma_load_3d(dst + b * (BNK * 128), tm, full, b * 64, j * BNK, bh);
                 if (++st == STAGES) { st = 0; ph ^= 1; }
+                PROF_ADD(6);
             }
             if (*abort) {  // drain our own copies before the CTA exits
                 for (uint32_t i = 0; i < (1u << 16) && !mbar_try_wait(q_full, 0); ++i) {}
@@ -1101,6 +1104,7 @@ int launch_tc(const void *q, const void *k, const void *v, const AttnArgs &args,
         const char *names[15] = {"sm wait s_full", "sm load S", "sm max+exp", "", "sm rescale+store P", "", "", "",
                                  "mma wait V", "mma wait p_full0", "mma issue S0", "mma wait p_full1", "mma issue PV1 S1", "mma wait K", "mma issue PV0"};
         if (KV_ROWS == 64) {
+            names[5] = "producer wait empty (per item x2)"; names[6] = "producer issue (per item x2)";
             names[8] = "S0 wait K"; names[9] = "S0 wait pv_done"; names[10] = "S0 issue"; names[11] = "PV wait V"; names[12] = "PV wait P0";
             names[13] = "PV issue 0 + wait P1"; names[14] = "PV issue 1";
         }

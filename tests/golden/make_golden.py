@@ -71,7 +71,8 @@ def sha(arr) -> np.ndarray:
 
 def main() -> None:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default=os.environ.get("ENCELADUS_REFERENCE", "/root/reference"))
+    ap.add_argument("--reference", default=os.environ.get("ENCELADUS_REFERENCE"), required="ENCELADUS_REFERENCE" not in os.environ,
+                    help="checkout of kashifulhaque/enceladus (or set ENCELADUS_REFERENCE)")
     ap.add_argument("--out", default=str(Path(__file__).parent))
     a = ap.parse_args()
     ex = import_reference(a.reference)

@@ -357,3 +357,34 @@ def test_warmup_and_explain_describe_the_native_kernel_without_launching(capsys)
         ops.softmax_kernel.warmup(x, x, 8, 8, 8, BLOCK=8, variant=99)
     with pytest.raises(TypeError):
         ops.softmax_kernel.warmup(x, x, 8)
+
+
+def test_piecewise_staging_plan_covers_every_unit_once_on_aligned_boundaries(monkeypatch):
+    """Host logic of the piecewise NumPy staging (no device needed): pieces tile the units exactly, start on
+    256-byte boundaries in every partitioned array, and arrays that cannot be cut fall back to one piece."""
+    from enceladus_b200 import ops
+    from enceladus_b200.runtime import jit
+
+    monkeypatch.setattr(jit, "PIPELINE_MIN_BYTES", 1)
+    monkeypatch.setattr(jit, "PIPELINE_PIECE_BYTES", 64 << 10)
+    ad = ops.layernorm_kernel.adapter()
+    m, n = 777, 1024
+    x = np.zeros((m, n), np.float16)
+    y, mean, rstd = np.empty_like(x), np.empty(m, np.float32), np.empty(m, np.float32)
+    w = np.zeros(n, np.float16)
+    bound = dict(x_ptr=x, y_ptr=y, w_ptr=w, b_ptr=w, mean_ptr=mean, rstd_ptr=rstd, stride_x=n, stride_y=n, n_cols=n, eps=1e-5, BLOCK=1024)
+    hosts = ["x_ptr", "y_ptr", "w_ptr", "b_ptr", "mean_ptr", "rstd_ptr"]
+    sp, pieces = jit._pipeline_plan(ad, bound, (m, 1, 1), hosts)
+    assert sum(c for _, c in pieces) == m and [u for u, _ in pieces] == sorted({u for u, _ in pieces}) and len(pieces) >= 2
+    assert all(u0 == pieces[i - 1][0] + pieces[i - 1][1] for i, (u0, _) in enumerate(pieces) if i)
+    for name, per in sp.arrays.items():
+        assert all((u0 * per * bound[name].itemsize) % 256 == 0 for u0, _ in pieces), name
+    assert set(sp.arrays) == {"x_ptr", "y_ptr", "mean_ptr", "rstd_ptr"}  # w and b are shared, staged once
+    # strided rows: the flat view would be a copy -> one piece
+    bound2 = dict(bound, x_ptr=np.zeros((m, 2 * n), np.float16)[:, :n], stride_x=2 * n)
+    assert jit._pipeline_plan(ad, bound2, (m, 1, 1), hosts) is None
+    # too little data -> one piece
+    monkeypatch.setattr(jit, "PIPELINE_MIN_BYTES", 1 << 30)
+    assert jit._pipeline_plan(ad, bound, (m, 1, 1), hosts) is None
+    # kernels without independent pieces have no split at all
+    assert ops.histogram_kernel.adapter().split is None
