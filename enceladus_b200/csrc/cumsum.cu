@@ -709,16 +709,17 @@ int launch_flat_ring(const void *in, void *out, int64_t n, const void *seed, cud
     FlatArgs a{in, out, n, seed, (unsigned long long *)(scr + 64), (unsigned *)scr, err,
                reinterpret_cast<uintptr_t>(out) % (4 * sizeof(TOut)) == 0 ? 1 : 0};
     const size_t tile_bytes = (size_t)RING_TILE * sizeof(TIn);
-    static const int ring_kb = getenv("ENC_SCAN_RING_KB") ? atoi(getenv("ENC_SCAN_RING_KB")) : 96;   // TUNING-ONLY
-    static const int ctas_per_sm = getenv("ENC_SCAN_CTAS") ? atoi(getenv("ENC_SCAN_CTAS")) : 2;      // TUNING-ONLY
-    int slots = (int)((ring_kb * 1024) / tile_bytes);  // about 96 KB of tiles per CTA, two CTAs per SM
+    // About 96 KB of tiles per CTA, two CTAs per SM.  Measured at 2^30 int32: throughput follows the bytes the rings
+    // hold per SM (2 x 64 KB: 64% of the copy bandwidth, 2 x 96 KB or 3 x 64 KB: 80%), not the number of scanner warps
+    // (one CTA with a 192 KB ring: 59%).
+    int slots = (int)((96 * 1024) / tile_bytes);
     if (slots > 16) slots = 16;
     if (slots < 2) slots = 2;
     const size_t smem = tile_bytes * slots;
     auto kern = scan_ring_kernel<TIn, Acc, TOut>;
     e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
     if (e != cudaSuccess) return fail(ENC_ERR_LAUNCH, "enc_cumsum: cannot opt in to shared memory: %s", cudaGetErrorString(e));
-    int64_t grid = (int64_t)device_props().sm_count * ctas_per_sm;
+    int64_t grid = (int64_t)device_props().sm_count * 2;
     if (grid > ntiles) grid = ntiles;
     kern<<<(unsigned)grid, RING_THREADS, smem, st>>>(a, slots);
     return check_launch("enc_cumsum");
