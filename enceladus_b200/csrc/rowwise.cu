@@ -121,6 +121,10 @@ __device__ __forceinline__ void process_row(const RowRegs<T, V> &x, const RowArg
     };
 
     constexpr float LOG2E = 1.4426950408889634f;
+    // Softmax needs every exponential twice (row sum, output).  For float32 rows they are kept in registers; for
+    // 16-bit rows, which sit packed in half as many registers, they are recomputed.
+    constexpr bool KEEP_EXP = OP == OP_SOFTMAX && sizeof(T) == 4;
+    float ex[KEEP_EXP ? V * NV : 1];
     float s0 = 1.0f, s1 = 0.0f;  // softmax: -max*log2e, 1/sum.  layernorm: rstd, -mean*rstd.  rmsnorm: rstd.
     if (OP == OP_SOFTMAX) {
         float m = -INFINITY;
@@ -139,7 +143,11 @@ __device__ __forceinline__ void process_row(const RowRegs<T, V> &x, const RowArg
             float f[NV];
             get(j, f);
 #pragma unroll
-            for (int e = 0; e < NV; ++e) s += fast_exp2(fmaf(f[e], LOG2E, nm));
+            for (int e = 0; e < NV; ++e) {
+                const float p = fast_exp2(fmaf(f[e], LOG2E, nm));
+                s += p;
+                if (KEEP_EXP) ex[j * NV + e] = p;  // float32 rows: the exponentials take the registers the row leaves
+            }
         }
         s0 = nm;
         s1 = __fdiv_rn(1.0f, group_reduce<false>(s, tpr, red1));
@@ -277,7 +285,7 @@ __device__ __forceinline__ void process_row(const RowRegs<T, V> &x, const RowArg
         } else {
 #pragma unroll
             for (int e = 0; e < NV; ++e) {
-                if (OP == OP_SOFTMAX) o[e] = fast_exp2(fmaf(f[e], LOG2E, s0)) * s1;
+                if (OP == OP_SOFTMAX) o[e] = (KEEP_EXP ? ex[j * NV + e] : fast_exp2(fmaf(f[e], LOG2E, s0))) * s1;
                 else if (OP == OP_LAYERNORM) o[e] = fmaf(fmaf(f[e], s0, s1), wv[e], bv[e]);
                 else o[e] = (f[e] * s0) * wv[e];
             }
