@@ -351,9 +351,12 @@ __device__ __forceinline__ Acc ring_tile_scan(Acc (&v)[QUADS][4], Acc *sh, int t
     return sh[QUADS * NW];
 }
 
-// Windows of 32 tile descriptors the resolver reads per round trip.  Measured at 2^30 int32: 1 -> 78% of the copy
-// bandwidth, 2 -> 80%, 4 -> 77%, 8 -> 71% (wider reads mostly fetch descriptors that are still empty).
-constexpr int RING_LOOK = 2;
+// Windows of 32 tile descriptors the resolver reads per round trip.  Measured at 2^30 int32: 1 -> 86% of the copy
+// bandwidth, 2 -> 80%, 4 -> 77%, 8 -> 71%: the nearest predecessors publish last, so wider reads mostly add loads
+// and polls of descriptors that a later round trip would have found ready.  (Two or three resolver warps taking
+// the ring visits in turn were measured too: 78% and 72% - concurrent look-backs find fewer finished prefixes
+// nearby and walk further.)
+constexpr int RING_LOOK = 1;
 
 __device__ __forceinline__ bool ring_wait(uint64_t *bar, uint32_t parity, unsigned *error) {
     for (uint32_t i = 0; i < (1u << 22); ++i)
