@@ -355,7 +355,8 @@ __device__ __forceinline__ Acc ring_tile_scan(Acc (&v)[QUADS][4], Acc *sh, int t
 // bandwidth, 2 -> 80%, 4 -> 77%, 8 -> 71%: the nearest predecessors publish last, so wider reads mostly add loads
 // and polls of descriptors that a later round trip would have found ready.  (Two or three resolver warps taking
 // the ring visits in turn were measured too: 78% and 72% - concurrent look-backs find fewer finished prefixes
-// nearby and walk further.)
+// nearby and walk further.  Requesting the next visit's window ahead of time lost as well, 81%: what is read
+// early is further from a finished prefix.)
 constexpr int RING_LOOK = 1;
 
 __device__ __forceinline__ bool ring_wait(uint64_t *bar, uint32_t parity, unsigned *error) {
