@@ -86,23 +86,23 @@ __device__ __forceinline__ void exp2_fma_pair(float x0, float x1, float &p0, flo
     p1 = __uint_as_float(__float_as_uint(q1) + (__float_as_uint(t1) << 23));
 }
 
-// One row of one score block, in registers: mask, running maximum with lazy rescale, probabilities in
-// place (float32 bit patterns), row sum.  `alpha` is the factor the accumulator must be scaled by (1 when
-// no rescale is due).  POLY_PAIRS = n: one pair of exponentials in n runs on the FMA pipes (0: none).
-template <int NCH, int POLY_PAIRS = 0>
-__device__ __forceinline__ void softmax_row(uint32_t (&sv)[NCH][32], float qk_scale, bool need_mask, int64_t n0, int64_t row,
-                                            int64_t seq, int causal, float &m_ref, float &l, float &alpha, bool &rescale) {
+// One row (or one part of a row) of one score block, in registers.  row_mask_max masks and returns the raw
+// maximum; row_exp turns the scores into probabilities in place (float32 bit patterns) against the running
+// maximum with lazy rescale and adds their sum to `l`.  `alpha` is the factor the accumulator must be scaled by
+// (1 when no rescale is due).  POLY_PAIRS = n: one pair of exponentials in n runs on the FMA pipes (0: none).
+// `col0` is the global key index of sv[0][0].
+template <int NCH>
+__device__ __forceinline__ float row_mask_max(uint32_t (&sv)[NCH][32], bool need_mask, int64_t col0, int64_t row, int64_t seq, int causal) {
     if (need_mask) {
 #pragma unroll
         for (int c = 0; c < NCH; ++c)
 #pragma unroll
             for (int i = 0; i < 32; ++i) {
-                const int64_t col = n0 + c * 32 + i;
+                const int64_t col = col0 + c * 32 + i;
                 if (col >= seq || (causal && col > row)) sv[c][i] = __float_as_uint(-INFINITY);
             }
     }
-    // row maximum of the raw scores (the scale is positive, so it commutes with the maximum); two chains of
-    // three-input maxima
+    // two chains of three-input maxima
     float mx0 = -INFINITY, mx1 = -INFINITY;
 #pragma unroll
     for (int c = 0; c < NCH; ++c)
@@ -111,7 +111,13 @@ __device__ __forceinline__ void softmax_row(uint32_t (&sv)[NCH][32], float qk_sc
             mx0 = max3(mx0, __uint_as_float(sv[c][i]), __uint_as_float(sv[c][i + 1]));
             mx1 = max3(mx1, __uint_as_float(sv[c][i + 2]), __uint_as_float(sv[c][i + 3]));
         }
-    const float mx = fmaxf(mx0, mx1) * qk_scale;
+    return fmaxf(mx0, mx1);
+}
+
+template <int NCH, int POLY_PAIRS>
+__device__ __forceinline__ void row_exp(uint32_t (&sv)[NCH][32], float qk_scale, float mx_raw, float &m_ref, float &l, float &alpha,
+                                        bool &rescale) {
+    const float mx = mx_raw * qk_scale;  // the scale is positive, so it commutes with the maximum
     const float m_new = fmaxf(m_ref, mx);
     // rescale only when the maximum moved far enough for exp2(s - m_ref) to risk overflow
     rescale = m_new > m_ref + RESCALE_THRESHOLD;  // also true for the first finite maximum
@@ -144,6 +150,13 @@ __device__ __forceinline__ void softmax_row(uint32_t (&sv)[NCH][32], float qk_sc
     float s0, s1;
     f2_unpack(f2_add(sum0, sum1), s0, s1);
     l = l * alpha + (s0 + s1);
+}
+
+template <int NCH, int POLY_PAIRS = 0>
+__device__ __forceinline__ void softmax_row(uint32_t (&sv)[NCH][32], float qk_scale, bool need_mask, int64_t n0, int64_t row,
+                                            int64_t seq, int causal, float &m_ref, float &l, float &alpha, bool &rescale) {
+    const float mx_raw = row_mask_max<NCH>(sv, need_mask, n0, row, seq, causal);
+    row_exp<NCH, POLY_PAIRS>(sv, qk_scale, mx_raw, m_ref, l, alpha, rescale);
 }
 
 // P row into shared memory in the swizzled K-major layout the MMA reads: 64-wide boxes, 128-byte rows,
@@ -703,6 +716,8 @@ attention_ts_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
 // softmax that has work queued.  A 128x64x16 MMA runs at two thirds of the rate of a 128x128x16 one, which
 // the removed idle time more than pays for.
 //   TMEM columns: tile t buffer b at t*128 + b*64 (S, then P in its first 32)   O0 [256,256+D)  O1 [384,384+D)
+//   (Two softmax threads per query row - 640 threads, the halves of a row meeting at a named barrier for the row
+//   maximum - were measured as well: 1098 against 1173 TFLOP/s, the exchange costs more than the shorter chain saves.)
 //   warp 0 = TMA producer, warps 1 and 2 = score issuers of tile 0 and 1 (S_t(j) goes out as soon as K(j) is
 //   there and P_t(j-2) V has left the buffer), warp 3 = P V issuer of both tiles; K and V have a ring each
 constexpr int BN64 = 64;
