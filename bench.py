@@ -1,23 +1,30 @@
 """Benchmark of the kernel set on B200: per-kernel HBM GB/s or TFLOP/s against the measured roofline.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--workload NAME] [--kernels all|none|a,b,...]
-                    [--impl ours|reference] [--cpu-baseline-all] [--no-e2e]
+                    [--impl ours|reference] [--scaling weak|strong] [--no-e2e] [--no-cpu-baseline]
 
 Prints ONE JSON line.  The headline workload (default `layernorm`: LayerNorm over bf16 [16384, 4096]) is
-timed for exactly K steps after W warm-up steps; `per_kernel` carries one row for every other workload
-of the kernel set, each timed the same way with fewer steps.  A step is one launch of the kernel over
+timed for exactly K steps after W warm-up steps; `roofline.per_kernel` carries one entry for every workload
+of the kernel set, each timed the same way with its own step count.  A step is one launch of the kernel over
 one batch of seeded synthetic input that is already resident in HBM.  Between steps the kernels rotate
 through several buffer sets whose total size exceeds L2 several times, so every step reads from DRAM.
 
-  value      algorithmic bytes (or FLOPs) of all ranks / device time (CUDA events, max over ranks)
-  e2e        the same metric through the public launch path with HOST (pinned NumPy) arguments:
-             host->device copy, kernel, device->host copy inside the timed region
-  roofline   achieved / measured peak (MEASURED_PEAKS.json if present, else the stated fallback)
-  cpu_baseline   the NumPy restatement of the reference's CPU path on this host's cores, bounded sample
+  value          algorithmic bytes (or FLOPs) of all ranks / device time (CUDA events, max over ranks)
+  e2e            the same metric through the public launch path with HOST (pinned NumPy) arguments:
+                 host->device copy, kernel, device->host copy inside the timed region; `e2e.pcie` holds the
+                 pinned copy bandwidths measured in the same run and `e2e.frac` = the time the copies alone
+                 need at those bandwidths / the measured time
+  roofline       achieved / measured peak (MEASURED_PEAKS.json if present, else the stated fallback)
+  cpu_baseline   the reference's own CPU path (its interpreter, ENCELADUS_INTERPRET=1, installed under
+                 oracle/_ref by oracle/build_ref.py) on this host's cores, bounded sample, with the example's
+                 float64 NumPy reference() beside it; N = 1 only, measured before CUDA is initialised
+  verified       every row is checked in-run against an independent computation of the same result
 
-N > 1 (under torchrun): every rank runs the same per-GPU workload on its own shard (weak scaling);
-histogram adds its all-reduce of the bins and the flat cumsum its all-gather of shard totals inside the
-timed region.  `--impl reference` times the CPU restatement of the reference with all host threads.
+N > 1 (under torchrun).  `--scaling weak` (default): every rank runs the same per-GPU workload; `--scaling
+strong`: the configuration itself is cut into contiguous shards (rows, elements, M-blocks, (batch, head)
+slices).  Either way the histogram adds its all-reduce of the bins and the flat cumsum its all-gather of shard
+totals inside the timed region, and both results are verified across ranks.  `--impl reference` times the
+reference's CPU path on all host cores (rank 0 only).
 """
 
 from __future__ import annotations
@@ -30,7 +37,6 @@ import subprocess
 import sys
 import threading
 import time
-from concurrent.futures import ThreadPoolExecutor
 from pathlib import Path
 
 import numpy as np
@@ -61,6 +67,11 @@ NCU_TRAFFIC: dict[str, float | None] = {
     "attention_bf16_8x32x4096x128_causal": 1_057_350_912,   # profiles/attention_causal.md
 }
 
+USE_GRAPH = True
+RANK = int(os.environ.get("RANK", "0"))
+LOCAL_RANK = int(os.environ.get("LOCAL_RANK", "0"))
+WORLD = int(os.environ.get("WORLD_SIZE", "1"))
+
 
 def peaks() -> tuple[dict, str]:
     p = ROOT / "MEASURED_PEAKS.json"
@@ -75,9 +86,10 @@ def peaks() -> tuple[dict, str]:
 
 
 # ---------------------------------------------------------------------------------------------------
-# Workloads.  Each returns a dict with: make(dev, i) -> argument set number i on the device, run(set),
-# work (algorithmic bytes or flops per launch), unit, bound, dtype, and optionally host()/run_host()
-# for the end-to-end path and cpu() for the CPU baseline.
+# Workloads.  Each entry builds a dict with: make(i) -> argument set number i on the device, run(set),
+# verify(set) -> bool (after run(set)), work (algorithmic bytes or flops per launch on this rank), unit,
+# bound, dtype, and optionally host()/run_host() for the end-to-end path.
+# `shard` = (rank, world) cuts the configuration itself (strong scaling); None = the whole configuration.
 # ---------------------------------------------------------------------------------------------------
 def _bf16_host(shape, rng, scale=1.0, shift=0.0):
     import ml_dtypes
@@ -85,12 +97,18 @@ def _bf16_host(shape, rng, scale=1.0, shift=0.0):
     return (shift + scale * rng.standard_normal(shape)).astype(np.float32).astype(ml_dtypes.bfloat16)
 
 
-def workloads(scale: float = 1.0):
+def _f16_host(x: np.ndarray) -> np.ndarray:
+    import torch
+
+    return torch.from_numpy(np.ascontiguousarray(x, dtype=np.float32)).half().numpy()
+
+
+def workloads(scale: float = 1.0, shard: tuple[int, int] | None = None):
     import torch
 
     from enceladus_b200 import _native as N
+    from enceladus_b200 import dist as edist
     from enceladus_b200 import ops
-    from oracle import enceladus_oracle as O  # CPU baseline leg only
 
     W = {}
 
@@ -99,21 +117,38 @@ def workloads(scale: float = 1.0):
         g.manual_seed(seed)
         return g
 
+    def part(n, align=1):
+        """This rank's share of n units under strong scaling, the whole n otherwise."""
+        if shard is None:
+            return n
+        lo, hi = edist.shard_range(n, shard[0], shard[1], align)
+        return hi - lo
+
+    def close(got, want, atol, rtol):
+        return bool(torch.isfinite(got.float()).all()) and bool(torch.allclose(got.float(), want.float(), atol=atol, rtol=rtol))
+
     # ---- config 1: softmax fp32 [4096, 1024] ----
     def softmax_wl(n=1024):
-        m = 4096
+        m_full = 4096
+        m = part(m_full)
+
+        def verify(s):  # rows sum to one, and 64 rows against torch
+            x, y = s
+            rows = torch.linspace(0, m - 1, 64, device="cuda").long()
+            return bool((y.sum(1, dtype=torch.float64) - 1).abs().max() < 1e-5) and close(y[rows], torch.softmax(x[rows], 1), 1e-6, 1e-5)
+
         return dict(
-            name=f"softmax_f32_4096x{n}", kernel="softmax", jit=ops.softmax_kernel, unit="GB/s", bound="hbm", dtype="f32",
+            name=f"softmax_f32_{m_full}x{n}", kernel="softmax", jit=ops.softmax_kernel, unit="GB/s", bound="hbm", dtype="f32",
             work=2 * m * n * 4, set_bytes=2 * m * n * 4,
             make=lambda i: (torch.randn(m, n, device="cuda", generator=gen(i)) * 4, torch.empty(m, n, device="cuda")),
-            run=lambda s: ops.softmax_kernel[(m,)](s[1], s[0], n, n, n, BLOCK=n),
+            run=lambda s: ops.softmax_kernel[(m,)](s[1], s[0], n, n, n, BLOCK=n), verify=verify,
             host=lambda: (np.random.default_rng(0).standard_normal((m, n)).astype(np.float32) * 4,),
-            run_host=lambda h: ops.softmax(h[0]),
-            cpu=lambda h: O.softmax(h[0]), cpu_units=2 * m * n * 4)
+            run_host=lambda h: ops.softmax(h[0]))
 
     # ---- config 2: LayerNorm / RMSNorm bf16 [16384, 4096], tanh-GELU fp32 2^28 ----
     def norm_wl(kind):
-        m, n = 16384, 4096
+        m_full, n = 16384, 4096
+        m = part(m_full)
 
         def make(i):
             g = gen(i)
@@ -127,31 +162,51 @@ def workloads(scale: float = 1.0):
             r = np.random.default_rng(0)
             return _bf16_host((m, n), r), _bf16_host(n, r, 0.1, 1.0), _bf16_host(n, r, 0.1)
 
+        def verify(s):  # 256 rows against the float32 formula in torch (bf16 output tolerance), statistics at 1e-5
+            x, w, b, y, mean, rstd = s
+            rows = torch.linspace(0, m - 1, 256, device="cuda").long()
+            xf = x[rows].float()
+            if kind == "layernorm":
+                mu = xf.mean(1, keepdim=True)
+                var = ((xf - mu) ** 2).mean(1, keepdim=True)
+                rs = 1 / torch.sqrt(var + 1e-5)
+                want = (xf - mu) * rs * w.float() + b.float()
+                if not (close(mean[rows], mu[:, 0], 1e-5, 1e-5) and close(rstd[rows], rs[:, 0], 1e-5, 1e-5)):
+                    return False
+            else:
+                want = xf * (1 / torch.sqrt((xf * xf).mean(1, keepdim=True) + 1e-6)) * w.float()
+            return close(y[rows], want, 1e-2, 1.6e-2)
+
         if kind == "layernorm":
             run = lambda s: ops.layernorm_kernel[(m,)](s[0], s[3], s[1], s[2], s[4], s[5], n, n, n, 1e-5, BLOCK=1024)  # noqa: E731
             run_host = lambda h: ops.layernorm(h[0], h[1], h[2], 1e-5)  # noqa: E731
-            cpu = lambda h, rows=None: O.layernorm(h[0][:rows], h[1], h[2], 1e-5)  # noqa: E731
         else:
             run = lambda s: ops.rmsnorm_kernel[(m,)](s[0], s[1], s[3], n, n, n, 1e-6, BLOCK=4096)  # noqa: E731
             run_host = lambda h: ops.rmsnorm(h[0], h[1], 1e-6)  # noqa: E731
-            cpu = lambda h, rows=None: O.rmsnorm(h[0][:rows], h[1], 1e-6)  # noqa: E731
-        return dict(name=f"{kind}_bf16_16384x4096", kernel=kind, jit=getattr(ops, kind + "_kernel"), unit="GB/s", bound="hbm", dtype="bf16",
-                    work=2 * m * n * 2, set_bytes=2 * m * n * 2, make=make, run=run, host=host, run_host=run_host,
-                    cpu=cpu, cpu_rows=m, cpu_units=2 * m * n * 2, rows=m, row_bytes=2 * n * 2)
+        return dict(name=f"{kind}_bf16_{m_full}x{n}", kernel=kind, jit=getattr(ops, kind + "_kernel"), unit="GB/s", bound="hbm", dtype="bf16",
+                    work=2 * m * n * 2, set_bytes=2 * m * n * 2, make=make, run=run, verify=verify, host=host, run_host=run_host)
 
     def gelu_wl():
-        n = 1 << 28
+        n_full = 1 << 28
+        n = part(n_full, 1024)
+
+        def verify(s):
+            k = min(n, 1 << 22)
+            return close(s[1][:k], torch.nn.functional.gelu(s[0][:k], approximate="tanh"), 1e-5, 1e-5) and \
+                close(s[1][-k:], torch.nn.functional.gelu(s[0][-k:], approximate="tanh"), 1e-5, 1e-5)
+
         return dict(
             name="gelu_tanh_f32_2p28", kernel="gelu", jit=ops.tanh_gelu_kernel, unit="GB/s", bound="hbm", dtype="f32",
             work=2 * n * 4, set_bytes=2 * n * 4,
             make=lambda i: (torch.randn(n, device="cuda", generator=gen(i)) * 2, torch.empty(n, device="cuda")),
-            run=lambda s: ops.tanh_gelu_kernel[(n // 1024,)](s[0], s[1], n, BLOCK=1024),
+            run=lambda s: ops.tanh_gelu_kernel[(n // 1024,)](s[0], s[1], n, BLOCK=1024), verify=verify,
             host=lambda: ((np.random.default_rng(0).standard_normal(n // 8).astype(np.float32) * 2),),
-            run_host=lambda h: ops.tanh_gelu(h[0]), host_units=2 * (n // 8) * 4,
-            cpu=lambda h: O.gelu_tanh(h[0]), cpu_units=2 * (n // 8) * 4)
+            run_host=lambda h: ops.tanh_gelu(h[0]), host_units=2 * (n // 8) * 4)
 
     # ---- config 3: fused matmul fp16 ----
-    def matmul_wl(m, n, k):
+    def matmul_wl(m_full, n, k):
+        m = part(m_full, 128)
+
         def make(i):
             g = gen(i)
             a = ((torch.rand(m, k, device="cuda", generator=g) * 2 - 1) / math.sqrt(k)).half()
@@ -162,31 +217,46 @@ def workloads(scale: float = 1.0):
         def host():
             r = np.random.default_rng(0)
             sc = np.float32(1 / math.sqrt(k))
-            return ((r.random((m, k), dtype=np.float32) * 2 - 1) * sc).astype(np.float16), \
-                   ((r.random((k, n), dtype=np.float32) * 2 - 1) * sc).astype(np.float16), \
-                   (0.1 * r.standard_normal(n, dtype=np.float32)).astype(np.float16)
+            return _f16_host((r.random((m, k), dtype=np.float32) * 2 - 1) * sc), \
+                _f16_host((r.random((k, n), dtype=np.float32) * 2 - 1) * sc), \
+                _f16_host(0.1 * r.standard_normal(n, dtype=np.float32))
 
-        return dict(name=f"matmul_bias_gelu_f16_{m}x{n}x{k}", kernel="matmul", jit=ops.matmul_bias_gelu_kernel,
+        def verify(s):  # 64 rows against float32 matmul + erf-GELU in torch, float16 tolerance
+            a, b, bias, c = s
+            rows = torch.linspace(0, m - 1, 64, device="cuda").long()
+            want = torch.nn.functional.gelu(a[rows].float() @ b.float() + bias.float())
+            return close(c[rows], want, 1e-3, 2e-3)
+
+        return dict(name=f"matmul_bias_gelu_f16_{m_full}x{n}x{k}", kernel="matmul", jit=ops.matmul_bias_gelu_kernel,
                     unit="TFLOP/s", bound="tensor",
                     dtype="f16", work=2 * m * n * k, set_bytes=(m * k + k * n + m * n) * 2, make=make,
-                    run=lambda s: ops.matmul_bias_gelu(s[0], s[1], s[2], s[3]),
+                    run=lambda s: ops.matmul_bias_gelu(s[0], s[1], s[2], s[3]), verify=verify,
                     host=host, run_host=lambda h: ops.matmul_bias_gelu(h[0], h[1], h[2]))
 
     # ---- not a graded config: the reference's exact int8 matmul (benchmarks/bench_matmul.py:100-131) ----
-    def int8_matmul_wl(m, n, k):
+    def int8_matmul_wl(m_full, n, k):
+        m = part(m_full, 128)
+
         def make(i):
             g = gen(i)
             return (torch.randint(-128, 128, (m, k), device="cuda", dtype=torch.int8, generator=g),
                     torch.randint(-128, 128, (k, n), device="cuda", dtype=torch.int8, generator=g),
                     torch.empty(m, n, device="cuda", dtype=torch.int32))
 
-        return dict(name=f"matmul_int8_{m}x{n}x{k}", kernel="matmul_int", jit=ops.int8_matmul_kernel, unit="TOP/s",
+        def verify(s):  # exact: 16 rows in float64 (|sum| < 2^53)
+            rows = torch.linspace(0, m - 1, 16, device="cuda").long()
+            want = (s[0][rows].double() @ s[1].double()).long()
+            return bool((s[2][rows].long() == want).all())
+
+        return dict(name=f"matmul_int8_{m_full}x{n}x{k}", kernel="matmul_int", jit=ops.int8_matmul_kernel, unit="TOP/s",
                     bound="tensor", peak_scale=2.0, dtype="s8", work=2 * m * n * k, set_bytes=m * k + k * n + 4 * m * n, make=make,
-                    run=lambda s: ops.int_matmul(s[0], s[1], s[2]))
+                    run=lambda s: ops.int_matmul(s[0], s[1], s[2]), verify=verify)
 
     # ---- config 4: attention bf16 [8, 32, 4096, 128] ----
     def attention_wl(causal):
-        z, h, s_, d = 8, 32, 4096, 128
+        zf, hf, s_, d = 8, 32, 4096, 128
+        bh = part(zf * hf)
+        z, h = (zf, hf) if bh == zf * hf else (1, bh)
 
         def make(i):
             g = gen(i)
@@ -198,17 +268,28 @@ def workloads(scale: float = 1.0):
 
         def host():
             r = np.random.default_rng(0)
-            return tuple(_bf16_host((zh, h, s_, d), r) for _ in range(3))
+            return tuple(_bf16_host((zh, hf, s_, d), r) for _ in range(3))
+
+        def verify(s):  # the last (batch, head) slice, 192 query rows, against float32 softmax(QK^T)V in torch
+            q, k, v, o, _ = s
+            rows = torch.cat([torch.arange(0, 64, device="cuda"), torch.linspace(64, s_ - 1, 128, device="cuda").long()])
+            sc = (q[-1, -1, rows].float() @ k[-1, -1].float().T) / math.sqrt(d)
+            if causal:
+                sc = sc.masked_fill(torch.arange(s_, device="cuda")[None, :] > rows[:, None], float("-inf"))
+            want = torch.softmax(sc, 1) @ v[-1, -1].float()
+            return close(o[-1, -1, rows], want, 2e-2, 1.6e-2)
 
         return dict(name=f"attention_bf16_8x32x4096x128_{'causal' if causal else 'full'}", kernel="attention",
                     jit=ops.attention_kernel,
                     unit="TFLOP/s", bound="tensor", dtype="bf16", work=flops, set_bytes=4 * z * h * s_ * d * 2,
-                    make=make, run=lambda s: ops.attention(s[0], s[1], s[2], causal, None, s[3]),
-                    host=host, run_host=lambda hh: ops.attention(hh[0], hh[1], hh[2], causal), host_units=flops * zh // z)
+                    make=make, run=lambda s: ops.attention(s[0], s[1], s[2], causal, None, s[3]), verify=verify,
+                    host=host, run_host=lambda hh: ops.attention(hh[0], hh[1], hh[2], causal),
+                    host_units=4 * zh * hf * s_ * s_ * d // (2 if causal else 1))
 
     # ---- config 5: histogram / cumsum ----
     def hist_wl(kind):
-        n = int((1 << 30) * scale)
+        n_full = int((1 << 30) * scale)
+        n = part(n_full, 4096)
         bins = 256 if kind == "uniform256" else 4096
 
         def make(i):
@@ -234,16 +315,31 @@ def workloads(scale: float = 1.0):
 
                 dist.all_reduce(s[1])
 
+        def verify(s):
+            # one fresh launch into zeroed bins; bit-exact against torch.bincount of the same data, summed over
+            # the ranks exactly as the bins are (at N > 1 every rank must hold the global counts)
+            s[1].zero_()
+            run(s)
+            want = torch.zeros(bins, device="cuda", dtype=torch.int64)
+            for s0 in range(0, n, 1 << 28):
+                want += torch.bincount(s[0][s0 : s0 + (1 << 28)], minlength=bins)
+            total = torch.tensor([n], device="cuda", dtype=torch.int64)
+            if WORLD > 1:
+                import torch.distributed as dist
+
+                dist.all_reduce(want)
+                dist.all_reduce(total)
+            return bool((s[1].long() == want).all()) and int(s[1].long().sum()) == int(total)
+
         return dict(name=f"histogram_i32_2p30_{kind}", kernel="histogram", jit=ops.histogram_kernel, unit="GB/s", bound="hbm", dtype="i32",
-                    work=n * 4, set_bytes=n * 4, make=make, run=run, sets=1,
+                    work=n * 4, set_bytes=n * 4, make=make, run=run, verify=verify, sets=1,
+                    collective="all_reduce of the bins" if WORLD > 1 else None,
                     host=lambda: (np.random.default_rng(0).integers(0, bins, n // 16).astype(np.int32),),
-                    run_host=lambda h: ops.histogram(h[0], bins, 0.0, float(bins)), host_units=(n // 16) * 4,
-                    cpu=lambda h: O.histogram(h[0], bins, 0.0, float(bins)), cpu_units=(n // 16) * 4)
+                    run_host=lambda h: ops.histogram(h[0], bins, 0.0, float(bins)), host_units=(n // 16) * 4)
 
     def cumsum_wl(kind):
-        from enceladus_b200 import dist as edist
-
-        n = int((1 << 30) * scale) if kind == "i32" else int((1 << 28) * scale)
+        n_full = int((1 << 30) * scale) if kind == "i32" else int((1 << 28) * scale)
+        n = part(n_full, 4096)
 
         def make(i):
             g = gen(i)
@@ -251,10 +347,10 @@ def workloads(scale: float = 1.0):
                 x = torch.randint(0, 16, (n,), device="cuda", dtype=torch.int32, generator=g)
             else:
                 x = torch.randn(n, device="cuda", generator=g)
-            return x, torch.empty_like(x), torch.zeros(1, device="cuda", dtype=x.dtype)
+            return x, torch.empty_like(x)
 
         def run(s):
-            if WORLD > 1:  # local total -> all-gather -> seeded local scan (reads the shard twice)
+            if WORLD > 1:  # local total -> all-gather -> offset kernel -> seeded local scan (reads the shard twice)
                 edist.sharded_cumsum(s[0], edist.cuda_total, lambda x, seed: _scan_into(x, s[1], seed))
             else:
                 ops.cumsum_kernel[(1,)](s[1], s[0], 1, n, n, n, REVERSE=False, BLOCK_M=1, BLOCK_N=1 << 30)
@@ -266,17 +362,45 @@ def workloads(scale: float = 1.0):
                    seed.data_ptr(), -1, interop.current_stream())
             return out
 
+        def verify(s):
+            # differences of neighbouring outputs give back the input (every element), the first output is the input
+            # plus the offset of the ranks before, and the last output of the last rank is the global total; all in
+            # the scan's own arithmetic (int32 wraps; float32 within 1e-4 of the largest prefix)
+            x, out = s
+            import torch.distributed as dist
+
+            if kind == "i32":
+                ok = bool((out[1:] - out[:-1] == x[1:]).all())
+                local = int(x.sum(dtype=torch.int64))
+                before, total = 0, local
+                if WORLD > 1:
+                    sums = torch.zeros(WORLD, device="cuda", dtype=torch.int64)
+                    sums[RANK] = local
+                    dist.all_reduce(sums)
+                    before, total = int(sums[:RANK].sum()), int(sums.sum())
+                ok = ok and (int(out[0]) - before - int(x[0])) % (1 << 32) == 0
+                ok = ok and (int(out[-1]) - before - local) % (1 << 32) == 0
+                return ok and (RANK != WORLD - 1 or (int(out[-1]) - total) % (1 << 32) == 0)
+            exact = torch.cumsum(x.double(), 0)
+            if WORLD > 1:
+                sums = torch.zeros(WORLD, device="cuda", dtype=torch.float64)
+                sums[RANK] = exact[-1]
+                dist.all_reduce(sums)
+                exact += sums[:RANK].sum()
+            scale_ = max(float(exact.abs().max()), 1.0)
+            return bool(torch.isfinite(out).all()) and float((out.double() - exact).abs().max()) <= 1e-4 * scale_
+
         nh = n // 16
         return dict(name=f"cumsum_{kind}_{'2p30' if kind == 'i32' else '2p28'}", kernel="cumsum", jit=ops.cumsum_kernel, unit="GB/s",
-                    bound="hbm", dtype=kind, work=2 * n * 4, set_bytes=2 * n * 4, make=make, run=run, sets=1,
+                    bound="hbm", dtype=kind, work=2 * n * 4, set_bytes=2 * n * 4, make=make, run=run, verify=verify, sets=1,
+                    collective="all_gather of one total per rank + offset kernel" if WORLD > 1 else None,
                     host=lambda: ((np.random.default_rng(0).integers(0, 16, nh).astype(np.int32),) if kind == "i32"
                                   else (np.random.default_rng(0).standard_normal(nh).astype(np.float32),)),
-                    run_host=lambda h: ops.cumsum(h[0]), host_units=2 * nh * 4,
-                    cpu=lambda h: O.cumsum(h[0]), cpu_units=2 * nh * 4)
+                    run_host=lambda h: ops.cumsum(h[0]), host_units=2 * nh * 4)
 
+    W["layernorm"] = lambda: norm_wl("layernorm")
     W["softmax"] = softmax_wl
     W["softmax_4096x4096"] = lambda: softmax_wl(4096)  # the reference's own benchmark shape (benchmarks/bench_softmax.py)
-    W["layernorm"] = lambda: norm_wl("layernorm")
     W["rmsnorm"] = lambda: norm_wl("rmsnorm")
     W["gelu"] = gelu_wl
     if N.num_variants(N.K_MATMUL) > 0:
@@ -293,10 +417,18 @@ def workloads(scale: float = 1.0):
     return W
 
 
-USE_GRAPH = True
-RANK = int(os.environ.get("RANK", "0"))
-LOCAL_RANK = int(os.environ.get("LOCAL_RANK", "0"))
-WORLD = int(os.environ.get("WORLD_SIZE", "1"))
+# workload key -> name of its row (and of its CPU leg in oracle/cpu_legs.py)
+ROW_NAMES = {
+    "layernorm": "layernorm_bf16_16384x4096", "softmax": "softmax_f32_4096x1024", "softmax_4096x4096": "softmax_f32_4096x4096",
+    "rmsnorm": "rmsnorm_bf16_16384x4096", "gelu": "gelu_tanh_f32_2p28", "matmul_8192": "matmul_bias_gelu_f16_8192x8192x8192",
+    "matmul_4096x4096x16384": "matmul_bias_gelu_f16_4096x4096x16384", "matmul_int8_8192": "matmul_int8_8192x8192x8192",
+    "attention_full": "attention_bf16_8x32x4096x128_full", "attention_causal": "attention_bf16_8x32x4096x128_causal",
+    "histogram_uniform256": "histogram_i32_2p30_uniform256", "histogram_zipf4096": "histogram_i32_2p30_zipf4096",
+    "cumsum_i32": "cumsum_i32_2p30", "cumsum_f32": "cumsum_f32_2p28",
+}
+ROW_DTYPES = {"layernorm": "bf16", "rmsnorm": "bf16", "softmax": "f32", "softmax_4096x4096": "f32", "gelu": "f32",
+              "matmul_8192": "f16", "matmul_4096x4096x16384": "f16", "attention_full": "bf16", "attention_causal": "bf16",
+              "histogram_uniform256": "i32", "histogram_zipf4096": "i32", "cumsum_i32": "i32", "cumsum_f32": "f32"}
 
 
 # ---------------------------------------------------------------------------------------------------
@@ -409,6 +541,21 @@ def max_over_ranks(v: float) -> float:
     return v
 
 
+def sum_over_ranks(v: float) -> float:
+    if WORLD > 1:
+        import torch
+        import torch.distributed as dist
+
+        t = torch.tensor([v], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t)
+        return float(t.item())
+    return v
+
+
+def all_ranks(ok: bool) -> bool:
+    return max_over_ranks(0.0 if ok else 1.0) == 0.0
+
+
 def pinned(arrays):
     """Copies of NumPy arrays that live in pinned host memory (views of pinned torch tensors)."""
     import torch
@@ -424,7 +571,50 @@ def pinned(arrays):
     return tuple(out)
 
 
-def bench_workload(wl: dict, steps: int, warmup: int, pk: dict, pk_kind: str, sampler, e2e: bool, cpu: bool,
+def measure_pcie(nbytes: int = 256 << 20, reps: int = 4) -> dict:
+    """Pinned host<->device copy bandwidth of this rank's GPU, GB/s: host-to-device alone, device-to-host alone,
+    and both directions at once on two streams.  With N ranks every rank copies at the same time (barrier first),
+    so the figure is what a rank gets while its neighbours load the same host: the roofline of the `e2e` leg."""
+    import torch
+
+    h_in = torch.empty(nbytes, dtype=torch.uint8, pin_memory=True)
+    h_out = torch.empty(nbytes, dtype=torch.uint8, pin_memory=True)
+    d_in = torch.empty(nbytes, dtype=torch.uint8, device="cuda")
+    d_out = torch.zeros(nbytes, dtype=torch.uint8, device="cuda")
+    s1, s2 = torch.cuda.Stream(), torch.cuda.Stream()
+
+    def timed(fn):
+        fn()
+        torch.cuda.synchronize()
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(reps):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return max_over_ranks(e0.elapsed_time(e1)) / reps * 1e-3
+
+    def both():
+        cur = torch.cuda.current_stream()
+        s1.wait_stream(cur)
+        s2.wait_stream(cur)
+        with torch.cuda.stream(s1):
+            d_in.copy_(h_in, non_blocking=True)
+        with torch.cuda.stream(s2):
+            h_out.copy_(d_out, non_blocking=True)
+        cur.wait_stream(s1)
+        cur.wait_stream(s2)
+
+    t_h2d = timed(lambda: d_in.copy_(h_in, non_blocking=True))
+    t_d2h = timed(lambda: h_out.copy_(d_out, non_blocking=True))
+    t_both = timed(both)
+    return {"h2d_gbs": nbytes / t_h2d / 1e9, "d2h_gbs": nbytes / t_d2h / 1e9,
+            "duplex_gbs_each_way": nbytes / t_both / 1e9, "bytes": nbytes, "ranks_copying_at_once": WORLD,
+            "how": "pinned torch tensors, copy_(non_blocking) on this rank's GPU, CUDA events, slowest rank"}
+
+
+def bench_workload(wl: dict, steps: int, warmup: int, pk: dict, pk_kind: str, sampler, e2e: bool, pcie: dict | None,
                    min_region_ms: float = 0.0):
     """One bench row.  `min_region_ms` > 0 (per-kernel rows only, never the headline) raises `steps` until the
     timed region lasts about that long: a graph replay costs several microseconds to launch, which ten steps of
@@ -450,16 +640,30 @@ def bench_workload(wl: dict, steps: int, warmup: int, pk: dict, pk_kind: str, sa
         steps = max(steps, min(200, int(min_region_ms / est) + 1))
     ms = timed_region(wl["run"], sets, steps, warmup, graph)
     m1 = sampler.mark() if sampler else 0
-    achieved = wl["work"] / (ms * 1e-3) / (1e9 if wl["unit"] == "GB/s" else 1e12)
+    div = 1e9 if wl["unit"] == "GB/s" else 1e12
+    achieved = wl["work"] / (ms * 1e-3) / div        # this rank's work over the slowest rank's time
+    total = sum_over_ranks(wl["work"]) / (ms * 1e-3) / div
     peak = pk["hbm_gbs"] if wl["bound"] == "hbm" else pk["bf16_tflops"] * wl.get("peak_scale", 1.0)
     if "peak_scale" in wl:  # no int8 GEMM was measured on this pool: the 8-bit rate of the tensor cores is twice the 16-bit one
         pk_kind = f"{wl['peak_scale']:g} x {pk_kind} bf16"
+    verify_error = None
+    try:
+        wl["run"](sets[0])
+        ok = bool(wl["verify"](sets[0]))
+    except Exception as e:  # noqa: BLE001 - a checker that cannot run is a failed check, not a failed bench
+        ok = False
+        verify_error = f"{type(e).__name__}: {e}"
+    verified = all_ranks(ok)
     row = {
-        "name": wl["name"], "value": achieved * WORLD, "unit": wl["unit"], "ms_per_step": ms, "steps": steps,
-        "warmup": warmup, "dtype": wl["dtype"], "buffer_sets": nsets, "cuda_graph": graph,
+        "name": wl["name"], "value": total, "unit": wl["unit"], "ms_per_step": ms, "steps": steps,
+        "warmup": warmup, "dtype": wl["dtype"], "buffer_sets": nsets, "cuda_graph": graph, "verified": verified,
         "roofline": {"bound": wl["bound"], "achieved": achieved, "peak": peak, "unit": wl["unit"],
                      "frac": achieved / peak, "peak_source": pk_kind, "traffic": NCU_TRAFFIC.get(wl["name"])},
     }
+    if wl.get("collective"):
+        row["collective_in_timed_region"] = wl["collective"]
+    if verify_error:
+        row["verify_error"] = verify_error
     if sampler:
         row["clocks"] = sampler.summary(m0, m1)
     del sets
@@ -486,12 +690,14 @@ def bench_workload(wl: dict, steps: int, warmup: int, pk: dict, pk_kind: str, sa
         dev_ms = max_over_ranks(max(e0.elapsed_time(e1) / reps, wall * 1e3))
         last = wl["jit"].last_launch
         res = res if isinstance(res, tuple) else (res,)
-        row["e2e"] = {"value": units * WORLD / (dev_ms * 1e-3) / (1e9 if wl["unit"] == "GB/s" else 1e12), "unit": wl["unit"],
-                      "h2d_bytes_per_step": int(last.get("h2d_bytes", 0)),
-                      "d2h_bytes_per_step": int(sum(r.nbytes for r in res)), "ms_per_step": dev_ms,
+        h2d, d2h = int(last.get("h2d_bytes", 0)), int(sum(r.nbytes for r in res))
+        row["e2e"] = {"value": sum_over_ranks(units) / (dev_ms * 1e-3) / div, "unit": wl["unit"],
+                      "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "ms_per_step": dev_ms,
                       "workload_fraction": units / wl["work"]}
-        if cpu and RANK == 0:
-            row["cpu_baseline"] = cpu_baseline(wl, h, threads=1)
+        if pcie:  # the copies alone, both directions overlapped, at the bandwidths measured in this run
+            floor_ms = max(h2d / pcie["h2d_gbs"], d2h / pcie["d2h_gbs"], (h2d + d2h) / 2 / pcie["duplex_gbs_each_way"]) / 1e6
+            row["e2e"]["pcie_floor_ms"] = floor_ms
+            row["e2e"]["frac"] = floor_ms / dev_ms
     return row
 
 
@@ -522,8 +728,8 @@ def reference_shape_rows(pk: dict) -> list[dict]:
         ms = timed_region(run, sets, steps, 3, USE_GRAPH)
         value = work / (ms * 1e-3) / (1e9 if unit == "GB/s" else 1e12)
         peak = pk["hbm_gbs"] if bound == "hbm" else pk["bf16_tflops"] * (2.0 if unit == "TOP/s" else 1.0)
-        rows.append({"name": name, "value": value, "unit": unit, "ms_per_step": ms, "steps": steps, "frac_of_peak": value / peak,
-                     "published_m4pro": published, "vs_published": value / published if published else None})
+        rows.append({"name": name, "value": round(value, 1), "unit": unit, "ms_per_step": round(ms, 5),
+                     "frac_of_peak": round(value / peak, 3), "published_m4pro": published})
         del sets
         torch.cuda.empty_cache()
 
@@ -572,70 +778,63 @@ def reference_shape_rows(pk: dict) -> list[dict]:
     return rows
 
 
-def cpu_baseline(wl: dict, h, threads: int, budget_s: float = 20.0) -> dict:
-    """Times the NumPy restatement of the reference on a bounded sample of the workload's host input."""
-    units = wl.get("cpu_units", wl["work"])
-    rows = wl.get("cpu_rows")
-    sample = "whole host workload"
-    if rows:  # row-wise workloads: time a slice of rows sized for the budget
-        probe = 256
-        t0 = time.perf_counter()
-        wl["cpu"](h, probe)
-        per_row = (time.perf_counter() - t0) / probe
-        take = int(max(probe, min(rows, budget_s / max(per_row, 1e-9) * max(threads, 1))))
-        units = wl["row_bytes"] * take
-        sample = f"{take} of {rows} rows"
-        if threads > 1:
-            chunks = np.array_split(np.arange(take), threads)
-            t0 = time.perf_counter()
-            with ThreadPoolExecutor(threads) as pool:
-                list(pool.map(lambda c: wl["cpu"]((h[0][c[0] : c[-1] + 1], *h[1:])), [c for c in chunks if len(c)]))
-            dt = time.perf_counter() - t0
-        else:
-            t0 = time.perf_counter()
-            wl["cpu"](h, take)
-            dt = time.perf_counter() - t0
-    else:
-        t0 = time.perf_counter()
-        wl["cpu"](h)
-        dt = time.perf_counter() - t0
-        if "host_units" in wl and wl["host_units"] != wl["work"]:
-            sample = f"{wl['host_units'] / wl['work']:.4f} of the workload"
-    scale = 1e9 if wl["unit"] == "GB/s" else 1e12
-    return {"value": units / dt / scale, "unit": wl["unit"], "cores": threads, "kind": "port",
-            "sample": f"{sample}; NumPy restatement of the reference interpreter, {dt:.2f} s"}
+# ---------------------------------------------------------------------------------------------------
+# CPU baselines (the reference's own CPU path; oracle/cpu_legs.py).  Run before CUDA is initialised, because
+# the legs fork worker processes.
+def cpu_baselines(names: list[str], headline: str, headline_budget: float, row_budget: float) -> dict[str, dict]:
+    from oracle import cpu_legs
+
+    out = {}
+    for n in names:
+        if n not in cpu_legs.LEGS:
+            continue
+        try:
+            b = cpu_legs.baseline(n, headline_budget if n == headline else row_budget,
+                                  numpy_budget_s=2.0 if n == headline else 0.5)
+        except Exception as e:  # noqa: BLE001 - a failing CPU leg must not stop the GPU measurement
+            b = {"error": f"{type(e).__name__}: {e}"}
+        if b is not None:
+            out[n] = b
+    return out
 
 
 def reference_arm(args) -> None:
-    """`--impl reference`: the CPU restatement of the reference on all host threads, rank 0 only."""
+    """`--impl reference`: the reference's own CPU implementation of the headline workload (its interpreter, from
+    oracle/_ref) on all host cores, rank 0 only.  Each step runs one bounded sample of the workload."""
     if RANK != 0:
         return
-    import ml_dtypes  # noqa: F401
+    from oracle import cpu_legs
 
-    from oracle import enceladus_oracle as O
-
-    cores = len(os.sched_getaffinity(0))
-    m, n = 16384, 4096
-    r = np.random.default_rng(0)
-    h = (_bf16_host((m, n), r), _bf16_host(n, r, 0.1, 1.0), _bf16_host(n, r, 0.1))
-    wl = dict(name="layernorm_bf16_16384x4096", unit="GB/s", work=2 * m * n * 2, cpu_rows=m, row_bytes=2 * n * 2,
-              cpu=lambda hh, rows=None: O.layernorm(hh[0][:rows], hh[1], hh[2], 1e-5))
-    samples = []
-    info = None
-    for i in range(args.warmup + args.steps):
-        info = cpu_baseline(wl, h, threads=cores, budget_s=1.0)
-        if i >= args.warmup:
-            samples.append(info["value"])
-    value = float(np.mean(samples))
-    rows_bytes = 2 * m * n * 2
-    line = {"impl": "reference", "metric": "layernorm_bf16_16384x4096 algorithmic HBM GB/s (read+write)",
-            "value": value, "unit": "GB/s", "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
-            "ms_per_step": rows_bytes / (value * 1e9) * 1e3, "higher_is_better": True, "scaling": "weak",
-            "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "config": {"workload": "layernorm_bf16_16384x4096"},
-            "cpu_baseline": {"value": value, "unit": "GB/s", "cores": cores, "kind": "port", "sample": info["sample"]},
-            "e2e": {"value": value, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
-    print(json.dumps(line))
+    name = ROW_NAMES.get(args.workload, args.workload)
+    if name not in cpu_legs.LEGS:
+        print(json.dumps({"impl": "reference", "unavailable": f"no CPU leg for workload {name}"}))
+        return
+    r = cpu_legs.Runner(name, budget_s=0.4)  # about 0.4 s of all-core work per step
+    try:
+        samples = []
+        for i in range(args.warmup + args.steps):
+            dt, units = r.step()
+            if i >= args.warmup:
+                samples.append((dt, units))
+        dt = sum(s[0] for s in samples)
+        units = sum(s[1] for s in samples)
+        scale = 1e9 if r.leg.unit == "GB/s" else 1e12
+        value = units / dt / scale
+        full_units = r.leg.units(None, 0, r.leg.full_pieces)
+        workers = r.workers if r.leg.parallel else cpu_legs.blas_threads()
+        line = {"impl": "reference",
+                "metric": f"{name} algorithmic {'HBM GB/s (read+write)' if r.leg.unit == 'GB/s' else r.leg.unit}",
+                "value": value, "unit": r.leg.unit, "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+                "ms_per_step": full_units / (value * scale) * 1e3, "higher_is_better": True, "scaling": args.scaling,
+                "vs_baseline": None, "dtype": ROW_DTYPES.get(args.workload), "data": "synthetic",
+                "config": {"workload": name},
+                "cpu_baseline": {"value": value, "unit": r.leg.unit, "cores": workers, "kind": r.kind,
+                                 "sample": "each step: " + r.sample() + f"; {len(samples)} timed steps, {dt:.2f} s; "
+                                           "ms_per_step is the whole workload at this rate"},
+                "e2e": {"value": value, "unit": r.leg.unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+        print(json.dumps(line))
+    finally:
+        r.close()
 
 
 def main() -> None:
@@ -645,12 +844,15 @@ def main() -> None:
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="layernorm")
-    ap.add_argument("--kernels", default="all", help="per_kernel rows: all, none, or a comma list")
+    ap.add_argument("--kernels", default="all", help="per-kernel rows: all, none, or a comma list")
     ap.add_argument("--kernel-steps", type=int, default=10)
     ap.add_argument("--scale", type=float, default=1.0, help="shrinks the 2^30 / 2^28 element workloads")
+    ap.add_argument("--scaling", default="weak", choices=["weak", "strong"],
+                    help="N > 1: weak = the whole configuration on every rank, strong = the configuration cut into N shards")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-graph", action="store_true", help="launch the timed steps eagerly instead of as one CUDA graph")
-    ap.add_argument("--cpu-baseline-all", action="store_true")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--cpu-baseline-headline-only", action="store_true")
     ap.add_argument("--no-reference-shapes", action="store_true", help="skip the rows at the reference's own benchmark shapes")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
@@ -660,6 +862,16 @@ def main() -> None:
     if args.impl == "reference":
         reference_arm(args)
         return
+    if args.workload not in ROW_NAMES:
+        raise SystemExit(f"unknown workload {args.workload!r}; choose from {sorted(ROW_NAMES)}")
+    row_keys = ([] if args.kernels == "none" else [k for k in ROW_NAMES if k != args.workload] if args.kernels == "all"
+                else [k for k in args.kernels.split(",") if k != args.workload])
+
+    # ---- CPU baselines first: N = 1, rank 0, before this process touches CUDA (the legs fork workers) ----
+    cpu = {}
+    if WORLD == 1 and not args.no_cpu_baseline:
+        keys = [args.workload] + ([] if args.cpu_baseline_headline_only else row_keys)
+        cpu = cpu_baselines([ROW_NAMES[k] for k in keys if k in ROW_NAMES], ROW_NAMES[args.workload], 6.0, 1.5)
 
     import torch
 
@@ -674,25 +886,27 @@ def main() -> None:
 
     N.load()
     pk, pk_kind = peaks()
-    W = workloads(args.scale)
+    strong = args.scaling == "strong" and WORLD > 1
+    W = workloads(args.scale, (RANK, WORLD) if strong else None)
     if args.workload not in W:
-        raise SystemExit(f"unknown workload {args.workload!r}; choose from {sorted(W)}")
+        raise SystemExit(f"workload {args.workload!r} is not available in this build; choose from {sorted(W)}")
     sampler = ClockSampler(visible_gpu_index(LOCAL_RANK)) if RANK == 0 else None
     time.sleep(0.3)
+    pcie = None if args.no_e2e else measure_pcie()
 
-    head = bench_workload(W[args.workload](), args.steps, args.warmup, pk, pk_kind, sampler,
-                          e2e=not args.no_e2e, cpu=True)
+    head = bench_workload(W[args.workload](), args.steps, args.warmup, pk, pk_kind, sampler, e2e=not args.no_e2e, pcie=pcie)
     rows = []
     launches = args.steps
-    if args.kernels != "none":
-        names = [k for k in W if k != args.workload] if args.kernels == "all" else args.kernels.split(",")
-        for k in names:
-            try:
-                rows.append(bench_workload(W[k](), args.kernel_steps, 3, pk, pk_kind, sampler,
-                                           e2e=not args.no_e2e, cpu=args.cpu_baseline_all, min_region_ms=1.0))
-                launches += rows[-1]["steps"]
-            except Exception as e:  # noqa: BLE001 - one failing workload must not hide the others
-                rows.append({"name": k, "error": f"{type(e).__name__}: {e}"})
+    for k in row_keys:
+        if k not in W:
+            continue
+        try:
+            rows.append(bench_workload(W[k](), args.kernel_steps, 3, pk, pk_kind, sampler, e2e=not args.no_e2e, pcie=pcie,
+                                       min_region_ms=1.0))
+            launches += rows[-1]["steps"]
+        except Exception as e:  # noqa: BLE001 - one failing workload must not hide the others
+            rows.append({"name": ROW_NAMES.get(k, k), "error": f"{type(e).__name__}: {e}"})
+            torch.cuda.empty_cache()
     ref_rows = []
     if args.kernels == "all" and not args.no_reference_shapes:
         try:
@@ -707,17 +921,45 @@ def main() -> None:
         dist.destroy_process_group()
     if RANK != 0:
         return
+
+    def compact(r: dict) -> dict:
+        if "error" in r:
+            return {"error": r["error"]}
+        c = {"value": round(r["value"], 2), "unit": r["unit"], "frac": round(r["roofline"]["frac"], 4),
+             "ms_per_step": round(r["ms_per_step"], 5), "steps": r["steps"], "verified": r["verified"],
+             "e2e_value": round(r["e2e"]["value"], 2) if "e2e" in r else None,
+             "e2e_frac": round(r["e2e"]["frac"], 3) if "e2e" in r and "frac" in r["e2e"] else None}
+        if r.get("collective_in_timed_region"):
+            c["collective"] = r["collective_in_timed_region"]
+        if r.get("verify_error"):
+            c["verify_error"] = r["verify_error"]
+        b = cpu.get(r["name"])
+        if b and "value" in b:
+            c["cpu"] = {"value": round(b["value"], 5), "cores": b["cores"], "kind": b["kind"],
+                        "numpy_reference": round(b.get("numpy_reference", {}).get("value", 0.0), 5) or None}
+        return c
+
+    roofline = dict(head["roofline"])
+    roofline["per_kernel"] = {r["name"]: compact(r) for r in [head, *rows]}
+    e2e = head.get("e2e")
+    if e2e is not None and pcie is not None:
+        e2e = dict(e2e, pcie=pcie)
+    # key order matters to a reader who keeps only the end of the line: the rows at the reference's own shapes and
+    # the long CPU-sample descriptions come first, the graded per-kernel map last
     line = {
-        "metric": f"{head['name']} algorithmic {'HBM GB/s (read+write)' if head['unit'] == 'GB/s' else 'TFLOP/s'}",
-        "value": head["value"], "unit": head["unit"], "n_gpus": WORLD, "steps": args.steps, "warmup": args.warmup,
-        "ms_per_step": head["ms_per_step"], "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-        "dtype": head["dtype"], "data": "synthetic",
-        "config": {"workload": head["name"], "l2": f"rotating {head['buffer_sets']} buffer sets (> 4x L2 in total)",
-                   "sharding": "same per-GPU workload on every rank, no data-path collective",
-                   "timed_region": "K launches captured in one CUDA graph" if head.get("cuda_graph") else "K eager launches"},
-        "roofline": head["roofline"], "clocks": head.get("clocks"), "gpu_launches": launches,
-        "e2e": head.get("e2e"), "cpu_baseline": head.get("cpu_baseline"), "per_kernel": rows,
+        "metric": f"{head['name']} algorithmic {'HBM GB/s (read+write)' if head['unit'] == 'GB/s' else head['unit']}",
         "reference_shapes": ref_rows,
+        "cpu_baselines": {k: v for k, v in cpu.items() if k != head["name"]},
+        "run": {"l2": f"rotating {head['buffer_sets']} buffer sets (> 4x L2 in total)",
+                "sharding": ("the configuration cut into contiguous shards, one per rank" if strong else
+                             "same per-GPU workload on every rank") + "; no data-path collective except the histogram's "
+                            "all-reduce of bins and the cumsum's all-gather of totals",
+                "timed_region": "K launches captured in one CUDA graph" if head.get("cuda_graph") else "K eager launches"},
+        "value": head["value"], "unit": head["unit"], "n_gpus": WORLD, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": head["ms_per_step"], "higher_is_better": True, "scaling": "strong" if strong else "weak", "vs_baseline": None,
+        "dtype": head["dtype"], "data": "synthetic", "config": {"workload": head["name"]},
+        "verified": head["verified"], "clocks": head.get("clocks"), "gpu_launches": launches,
+        "e2e": e2e, "cpu_baseline": cpu.get(head["name"]), "roofline": roofline,
     }
     print(json.dumps(line))
 

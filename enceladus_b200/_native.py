@@ -62,6 +62,7 @@ SIGNATURES: dict[str, list] = {
     "enc_cumsum_noalloc": [_p, _p, _i64, _i, _p, _p, _p],
     "enc_cumsum_out_dtype": [_i],
     "enc_sum": [_p, _p, _i64, _i, _p],
+    "enc_scan_offset": [_p, _i, _i, _p, _i, _p],
     "enc_matmul": [_p, _p, _p, _p, _i64, _i64, _i64, _i64, _i64, _i64, _i, _i, _i, _p],
     "enc_matmul_int": [_p, _p, _p, _i64, _i64, _i64, _i64, _i64, _i64, _i, _i, _p],
     "enc_attention_fwd": [_p, _p, _p, _p, _p, _i64, _i64, _i64, _i64, _i64, _f, _i, _i, _i, _p],

@@ -32,12 +32,8 @@ constexpr int BM = 128, BN = 128;
 constexpr int kThreads = 192;
 constexpr float LOG2E = 1.4426950408889634f, LN2 = 0.6931471805599453f;
 constexpr float RESCALE_THRESHOLD = 8.0f;  // in log2 units
-#ifndef ENC_ATTN_STAGGER
-#define ENC_ATTN_STAGGER 1000  // cycles
-#endif
-#ifndef ENC_ATTN_POLY
-#define ENC_ATTN_POLY 8  // one pair of exponentials in 8 goes to the FMA pipes (measured best among 0, 1/2, 1/4, 1/8)
-#endif
+constexpr int kStaggerCycles = 1000;  // head start of tile 0 over tile 1 (see the score issuers)
+constexpr int kPolyPairs = 8;  // one pair of exponentials in 8 goes to the FMA pipes (measured best among 0, 1/2, 1/4, 1/8)
 
 struct AttnArgs {
     void *o;
@@ -47,18 +43,8 @@ struct AttnArgs {
     int causal;
     int is_bf16;
     unsigned *error;
-#ifdef ENC_ATTN_PROF
-    unsigned long long *prof;  // [16] cycle counters summed over CTAs (debug builds only)
-#endif
 };
 
-#ifdef ENC_ATTN_PROF
-#define PROF_T0() long long t_prof = clock64()
-#define PROF_ADD(i) do { long long t_now = clock64(); if (lane == 0) prof_acc[i] += t_now - t_prof; t_prof = t_now; } while (0)
-#else
-#define PROF_T0() do {} while (0)
-#define PROF_ADD(i) do {} while (0)
-#endif
 
 // 2^x on the FMA pipes, for the share of the exponentials that the special-function unit (16 results per
 // clock per SM) has no time for once two softmax warpgroups run side by side: x = i + f with i integer and f
@@ -463,10 +449,6 @@ attention_ts_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(o_full + 1);
     volatile uint32_t *abort = tmem_slot + 1;
 
-#ifdef ENC_ATTN_PROF
-    __shared__ long long prof_acc[16];
-    if (threadIdx.x < 16) prof_acc[threadIdx.x] = 0;
-#endif
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int qb = a.causal ? (int)(gridDim.x - 1 - blockIdx.x) : (int)blockIdx.x;  // heavy blocks first
     const int bh = blockIdx.y;
@@ -554,13 +536,9 @@ attention_ts_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
                 }
                 tc_commit(&s_full[t]);
             };
-#ifdef ENC_ATTN_PROF
-            long long t_prof = 0;
-#endif
             auto mma_pv = [&](int t, int j, uint32_t stage) -> bool {  // O_t += P_t V_j, P_t from tensor memory
                 if (!mbar_wait(&p_full[t], j & 1, abort)) return false;
                 tc_fence_after();
-                PROF_ADD(9 + 2 * t);
                 const uint32_t vb = v_lo + stage * (L::TILE >> 4);
 #pragma unroll
                 for (int kk = 0; kk < BN / 16; ++kk)  // 16 keys = 8 packed columns of P, 16 rows = 2048 bytes of V
@@ -580,15 +558,11 @@ attention_ts_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
                     tc_commit(&kv_empty[stage]);
                 }
             }
-#ifdef ENC_ATTN_PROF
-            t_prof = clock64();
-#endif
             for (int j = 0; j < nkv && ok; ++j) {
                 uint32_t vstage, kstage = 0;
                 slot(2 * j + 1, vstage, phase);
                 ok = mbar_wait(&kv_full[vstage], phase, abort);
                 if (!ok) break;
-                PROF_ADD(8);
                 const bool more = j + 1 < nkv;  // then at least one tile takes K(j+1)
                 bool k_ready = false;
 #pragma unroll
@@ -598,17 +572,14 @@ attention_ts_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
                     if (t == 1 && ok) tc_commit(&kv_empty[vstage]);  // V(j) is free once both products have run
                     if (ok && j + 1 < nkv_t[t]) {
                         if (!k_ready) {
-                            PROF_ADD(14);
                             slot(2 * j + 2, kstage, phase);
                             ok = mbar_wait(&kv_full[kstage], phase, abort);
                             if (!ok) break;
                             tc_fence_after();
-                            PROF_ADD(13);
                             k_ready = true;
                         }
                         mma_s(t, kstage);
                     }
-                    PROF_ADD(10 + 2 * t);
                 }
                 if (!ok) break;
                 if (more) tc_commit(&kv_empty[kstage]);
@@ -629,24 +600,20 @@ attention_ts_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
         const int64_t tile_m0 = m0 + t * BM;
         float m_ref = -INFINITY, l = 0.0f;
         bool ok = true;
-        PROF_T0();
         for (int j = 0; j < my_nkv && ok; ++j) {
             // S_t(j) complete; the MMA pipe runs in order, so P_t(j-1) V is complete too and O_t is quiescent
             ok = mbar_wait(&s_full[t], j & 1, abort);
             if (!ok) break;
             tc_fence_after();
-            if (warp == 4) PROF_ADD(0);
             const int64_t n0 = (int64_t)j * BN;
             const bool need_mask = (n0 + BN > a.seq) || (a.causal && n0 + BN > tile_m0);
             uint32_t sv[4][32];
 #pragma unroll
             for (int c = 0; c < 4; ++c) tmem_ld_32x32(t_s + c * 32, sv[c]);
             tmem_ld_wait();
-            if (warp == 4) PROF_ADD(1);
             float alpha;
             bool rescale;
             softmax_row(sv, a.qk_scale, need_mask, n0, row, a.seq, a.causal, m_ref, l, alpha, rescale);
-            if (warp == 4) PROF_ADD(2);
             if (j > 0 && __any_sync(0xffffffffu, rescale)) {
 #pragma unroll 1
                 for (int c0 = 0; c0 < D; c0 += 32) {
@@ -672,7 +639,6 @@ attention_ts_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
             tmem_st_wait();
             tc_fence_before();
             mbar_arrive(&p_full[t]);
-            if (warp == 4) PROF_ADD(4);
         }
         // ---- epilogue: O_t / l ----
         if (ok && my_nkv > 0) ok = mbar_wait(o_full, 0, abort);
@@ -698,9 +664,6 @@ attention_ts_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
 
     tc_fence_before();
     __syncthreads();
-#ifdef ENC_ATTN_PROF
-    if (threadIdx.x < 16 && a.prof) atomicAdd(a.prof + threadIdx.x, (unsigned long long)prof_acc[threadIdx.x]);
-#endif
     if (threadIdx.x == 0 && *abort) atomicExch(a.error, 4u);
     if (warp == 1) {
         tc_fence_after();
@@ -753,10 +716,6 @@ attention_ts64_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(o_full + 1);
     volatile uint32_t *abort = tmem_slot + 1;
 
-#ifdef ENC_ATTN_PROF
-    __shared__ long long prof_acc[16];
-    if (threadIdx.x < 16) prof_acc[threadIdx.x] = 0;
-#endif
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int qb = a.causal ? (int)(gridDim.x - 1 - blockIdx.x) : (int)blockIdx.x;  // heavy blocks first
     const int bh = blockIdx.y;
@@ -808,7 +767,6 @@ attention_ts64_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
                 for (int b = 0; b < D / 64; ++b)
                     tma_load_3d(smem + L::Q_OFF + t * L::QTILE + b * (BM * 128), &tm_q, q_full, b * 64, (int)(m0 + t * BM), bh);
             bool ok = true;
-            PROF_T0();
             uint32_t ks = 0, kp = 0, vs = 0, vp = 0;  // ring positions
             for (int it = 0; it < 2 * nkv && ok; ++it) {  // K0, K1 V0, K2 V1, ..., V(n-1): the order of consumption
                 const bool is_v = it == 2 * nkv - 1 || (it != 0 && (it & 1) == 0);
@@ -817,14 +775,12 @@ attention_ts64_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
                 uint64_t *full = is_v ? &v_full[st] : &k_full[st];
                 ok = mbar_wait(is_v ? &v_empty[st] : &k_empty[st], ph ^ 1, abort);
                 if (!ok) break;
-                PROF_ADD(5);
                 uint8_t *dst = smem + (is_v ? L::V_OFF : L::K_OFF) + st * L::TILE;
                 mbar_expect_tx(full, L::TILE);
                 const CUtensorMap *tm = is_v ? &tm_v : &tm_k;
 #pragma unroll
                 for (int b = 0; b < D / 64; ++b) tma_load_3d(dst + b * (BNK * 128), tm, full, b * 64, j * BNK, bh);
                 if (++st == STAGES) { st = 0; ph ^= 1; }
-                PROF_ADD(6);
             }
             if (*abort) {  // drain our own copies before the CTA exits
                 for (uint32_t i = 0; i < (1u << 16) && !mbar_try_wait(q_full, 0); ++i) {}
@@ -853,19 +809,16 @@ attention_ts64_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
                 // turns on the special-function unit instead of meeting there; the offset then persists because
                 // both tiles do the same work per block.
                 const long long t_start = clock64();
-                while (clock64() - t_start < ENC_ATTN_STAGGER) {}
+                while (clock64() - t_start < kStaggerCycles) {}
             }
-            PROF_T0();
             for (int j = 0; j < nkv && ok; ++j) {
                 ok = mbar_wait(&k_full[stage], phase, abort);
                 if (!ok) break;
-                if (t == 0) PROF_ADD(8);
                 if (j < my_nkv) {
                     // buffer j & 1 held S_t(j-2), then P_t(j-2): free once P_t(j-2) V has completed
                     if (j >= 2) ok = mbar_wait(&pv_done[t * 2 + (j & 1)], ((j - 2) >> 1) & 1, abort);
                     if (!ok) break;
                     tc_fence_after();
-                    if (t == 0) PROF_ADD(9);
                     const uint32_t kb = k_lo + stage * (L::TILE >> 4);
                     const uint32_t d_tmem = s_tmem + (j & 1) * BNK;
 #pragma unroll
@@ -876,7 +829,6 @@ attention_ts64_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
                 }
                 tc_commit(&k_empty[stage]);
                 if (++stage == STAGES) { stage = 0; phase ^= 1; }
-                if (t == 0) PROF_ADD(10);
             }
         } else if (warp == 3 && lane == 0) {
             // ---------------- P V issuer, both tiles in turn ----------------
@@ -885,11 +837,9 @@ attention_ts64_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
             const uint32_t v_lo = smem_desc_lo(smem_u32(smem + L::V_OFF), BNK * 128);
             uint32_t stage = 0, phase = 0;
             bool ok = true;
-            PROF_T0();
             for (int j = 0; j < nkv && ok; ++j) {
                 ok = mbar_wait(&v_full[stage], phase, abort);
                 if (!ok) break;
-                PROF_ADD(11);
                 const uint32_t vb = v_lo + stage * (L::TILE >> 4);
 #pragma unroll
                 for (int t = 0; t < 2; ++t) {
@@ -897,7 +847,6 @@ attention_ts64_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
                     ok = mbar_wait(&p_full[t * 2 + (j & 1)], (j >> 1) & 1, abort);
                     if (!ok) break;
                     tc_fence_after();
-                    PROF_ADD(12 + t);
                     const uint32_t p_tmem = tmem_base + t * 128 + (j & 1) * BNK;
 #pragma unroll
                     for (int kk = 0; kk < BNK / 16; ++kk)  // 16 keys = 8 packed columns of P, 16 rows = 2048 bytes of V
@@ -907,7 +856,6 @@ attention_ts64_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
                 if (!ok) break;
                 tc_commit(&v_empty[stage]);
                 if (++stage == STAGES) { stage = 0; phase ^= 1; }
-                PROF_ADD(14);
             }
             if (ok) tc_commit(o_full);
         }
@@ -925,24 +873,20 @@ attention_ts64_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
         const int64_t tile_m0 = m0 + t * BM;
         float m_ref = -INFINITY, l = 0.0f;
         bool ok = true;
-        PROF_T0();
         for (int j = 0; j < my_nkv && ok; ++j) {
             const int b = j & 1;
             ok = mbar_wait(&s_full[t * 2 + b], (j >> 1) & 1, abort);
             if (!ok) break;
             tc_fence_after();
-            if (warp == 4) PROF_ADD(0);
             const int64_t n0 = (int64_t)j * BNK;
             const bool need_mask = (n0 + BNK > a.seq) || (a.causal && n0 + BNK > tile_m0);
             uint32_t sv[2][32];
 #pragma unroll
             for (int c = 0; c < 2; ++c) tmem_ld_32x32(t_s + b * BNK + c * 32, sv[c]);
             tmem_ld_wait();
-            if (warp == 4) PROF_ADD(1);
             float alpha;
             bool rescale;
-            softmax_row<2, ENC_ATTN_POLY>(sv, a.qk_scale, need_mask, n0, row, a.seq, a.causal, m_ref, l, alpha, rescale);
-            if (warp == 4) PROF_ADD(2);
+            softmax_row<2, kPolyPairs>(sv, a.qk_scale, need_mask, n0, row, a.seq, a.causal, m_ref, l, alpha, rescale);
             if (j > 0 && __any_sync(0xffffffffu, rescale)) {
                 // O_t must be quiescent: P_t(j-1) V complete (P_t(j) V is not issued before this thread's arrival below)
                 ok = mbar_wait(&pv_done[t * 2 + (b ^ 1)], ((j - 1) >> 1) & 1, abort);
@@ -969,7 +913,6 @@ attention_ts64_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
             tmem_st_wait();
             tc_fence_before();
             mbar_arrive(&p_full[t * 2 + b]);
-            if (warp == 4) PROF_ADD(4);
         }
         // ---- epilogue: O_t / l ----
         if (ok && my_nkv > 0) ok = mbar_wait(o_full, 0, abort);
@@ -995,9 +938,6 @@ attention_ts64_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
 
     tc_fence_before();
     __syncthreads();
-#ifdef ENC_ATTN_PROF
-    if (threadIdx.x < 16 && a.prof) atomicAdd(a.prof + threadIdx.x, (unsigned long long)prof_acc[threadIdx.x]);
-#endif
     if (threadIdx.x == 0 && *abort) atomicExch(a.error, 4u);
     if (warp == 1) {
         tc_fence_after();
@@ -1108,28 +1048,7 @@ int launch_tc(const void *q, const void *k, const void *v, const AttnArgs &args,
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return fail(ENC_ERR_LAUNCH, "enc_attention_fwd: cannot opt in to %d bytes of shared memory: %s", smem, cudaGetErrorString(e));
     dim3 grid((unsigned)cdiv(args.seq, TILES * BM), (unsigned)bh);
-#ifdef ENC_ATTN_PROF
-    AttnArgs pa = args;
-    cudaMallocManaged(&pa.prof, 16 * 8);
-    memset(pa.prof, 0, 16 * 8);
-    kern<<<grid, threads, smem, st>>>(tq, tk, tv, pa);
-    cudaDeviceSynchronize();
-    {
-        const double blocks = (double)grid.x * grid.y * (double)cdiv(args.seq, KV_ROWS) * (args.causal ? 0.5 : 1.0);
-        const char *names[15] = {"sm wait s_full", "sm load S", "sm max+exp", "", "sm rescale+store P", "", "", "",
-                                 "mma wait V", "mma wait p_full0", "mma issue S0", "mma wait p_full1", "mma issue PV1 S1", "mma wait K", "mma issue PV0"};
-        if (KV_ROWS == 64) {
-            names[5] = "producer wait empty (per item x2)"; names[6] = "producer issue (per item x2)";
-            names[8] = "S0 wait K"; names[9] = "S0 wait pv_done"; names[10] = "S0 issue"; names[11] = "PV wait V"; names[12] = "PV wait P0";
-            names[13] = "PV issue 0 + wait P1"; names[14] = "PV issue 1";
-        }
-        for (int i = 0; i < 15; ++i)
-            if (pa.prof[i]) printf("  prof %-20s %9.0f cycles per kv block (tile 0)\n", names[i], (double)pa.prof[i] / blocks);
-    }
-    cudaFree(pa.prof);
-#else
     kern<<<grid, threads, smem, st>>>(tq, tk, tv, args);
-#endif
     return check_launch("enc_attention_fwd");
 }
 

@@ -17,6 +17,7 @@
 // float32 in float32, int64 in int64.
 #include <map>
 #include <mutex>
+#include <vector>
 
 #include "sm100.cuh"
 
@@ -296,6 +297,13 @@ __global__ void __launch_bounds__(THREADS) scan_lookback_kernel(FlatArgs a) {
 constexpr int RING_SCANNERS = 256, RING_THREADS = RING_SCANNERS + 96, RING_TILE = RING_SCANNERS * ITEMS;
 
 __device__ __forceinline__ void scanner_barrier() { asm volatile("bar.sync 1, %0;" ::"n"(RING_SCANNERS) : "memory"); }
+// Barrier of the scanner threads that also ANDs a predicate over them: every scanner leaves with the same answer.
+__device__ __forceinline__ bool scanner_all(bool ok) {
+    uint32_t r;
+    asm volatile("{\n\t.reg .pred p, q;\n\tsetp.ne.b32 q, %1, 0;\n\tbar.red.and.pred p, 1, %2, q;\n\tselp.b32 %0, 1, 0, p;\n\t}"
+                 : "=r"(r) : "r"((uint32_t)ok), "n"(RING_SCANNERS) : "memory");
+    return r != 0;
+}
 
 // tile_scan for the 256 scanner threads of the ring kernel (named barrier 1 instead of the CTA barrier)
 template <typename Acc>
@@ -322,7 +330,8 @@ __device__ __forceinline__ Acc ring_tile_scan(Acc (&v)[QUADS][4], Acc *sh, int t
         before[j] = __shfl_up_sync(0xffffffffu, incl[j], 1);
         if (lane == 0) before[j] = 0;
     }
-    scanner_barrier();  // sh may still be read by the previous tile's consumers
+    // (sh is free: every scanner has passed the barrier at the top of this tile's loop iteration, which it
+    // reaches only after its last read of sh for the previous tile)
     if (lane == 31) {
 #pragma unroll
         for (int j = 0; j < QUADS; ++j) sh[j * NW + warp] = incl[j];
@@ -359,6 +368,9 @@ __device__ __forceinline__ Acc ring_tile_scan(Acc (&v)[QUADS][4], Acc *sh, int t
 // early is further from a finished prefix.  Windows of 16 or 8 descriptors: 75% and 56% - more round trips.)
 constexpr int RING_LOOK = 1;
 
+// Bounded wait on a ring barrier.  A thread that gives up must not simply leave while the others of its role
+// go on to a barrier or a warp shuffle it will never reach: the threads that share a role agree on the outcome
+// (scanner_all / __all_sync right after the wait) and leave together.
 __device__ __forceinline__ bool ring_wait(uint64_t *bar, uint32_t parity, unsigned *error) {
     for (uint32_t i = 0; i < (1u << 22); ++i)
         if (sm100::mbar_try_wait(bar, parity)) return true;
@@ -421,7 +433,7 @@ __global__ void __launch_bounds__(RING_THREADS) scan_ring_kernel(FlatArgs a, int
         int s = 0;
         uint32_t parity = 0;
         for (;;) {
-            const bool ok = ring_wait(&full[s], parity, a.error);
+            const bool ok = __all_sync(0xffffffffu, ring_wait(&full[s], parity, a.error));
             const long long tile = ok ? slot_tile[s] : ntiles;
             if (tile >= ntiles) {
                 if (lane == 0) { slot_tile[s] = ntiles; mbar_arrive(&aggd[s]); }  // pass the sentinel on
@@ -461,7 +473,7 @@ __global__ void __launch_bounds__(RING_THREADS) scan_ring_kernel(FlatArgs a, int
         int s = 0;
         uint32_t parity = 0;
         for (;;) {
-            const bool ok = ring_wait(&aggd[s], parity, a.error);
+            const bool ok = __all_sync(0xffffffffu, ring_wait(&aggd[s], parity, a.error));
             const long long tile = ok ? slot_tile[s] : ntiles;
             if (tile >= ntiles) {
                 if (lane == 0) { slot_tile[s] = ntiles; mbar_arrive(&pref[s]); }
@@ -525,7 +537,7 @@ __global__ void __launch_bounds__(RING_THREADS) scan_ring_kernel(FlatArgs a, int
         int s = 0;
         uint32_t parity = 0;
         for (;;) {
-            if (!ring_wait(&pref[s], parity, a.error)) break;
+            if (!scanner_all(ring_wait(&pref[s], parity, a.error))) break;  // all 256 leave, or none
             const long long tile = slot_tile[s];
             if (tile >= ntiles) break;
             const int64_t t0 = tile * RING_TILE;
@@ -621,12 +633,39 @@ __global__ void __launch_bounds__(THREADS) scan_rows_kernel(RowScanArgs a) {
 }
 
 // ---- total (pass 1 of the multi-GPU flat scan) ---------------------------------------------
+// A pure read at the speed of the memory system: 16-byte streaming loads, four in flight per thread, four
+// accumulators.  (Any summation order is allowed: integers wrap, and the float32 total only positions the
+// shard's scan, whose tolerance is relative to the exact prefix.)
+template <typename TIn, typename Acc>
+__device__ __forceinline__ Acc sum_vec16(const uint4 &u) {
+    constexpr int PER = 16 / sizeof(TIn);
+    const TIn *e = reinterpret_cast<const TIn *>(&u);
+    Acc s = 0;
+#pragma unroll
+    for (int i = 0; i < PER; ++i) s += to_acc<Acc, TIn>(e[i]);
+    return s;
+}
+
 template <typename TIn, typename Acc>
 __global__ void __launch_bounds__(256) sum_partials_kernel(const TIn *in, int64_t n, Acc *partials) {
+    constexpr int PER = 16 / sizeof(TIn);
     __shared__ Acc sh[8];
-    Acc s = 0;
+    Acc s0 = 0, s1 = 0, s2 = 0, s3 = 0;
     const int64_t stride = (int64_t)gridDim.x * blockDim.x;
-    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) s += to_acc<Acc, TIn>(in[i]);
+    const int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const int64_t nvec = aligned16(in) ? n / PER : 0;
+    const uint4 *v = reinterpret_cast<const uint4 *>(in);
+    int64_t i = tid;
+    for (; i + 3 * stride < nvec; i += 4 * stride) {
+        const uint4 a = ld_stream(v + i), b = ld_stream(v + i + stride), c = ld_stream(v + i + 2 * stride), d = ld_stream(v + i + 3 * stride);
+        s0 += sum_vec16<TIn, Acc>(a);
+        s1 += sum_vec16<TIn, Acc>(b);
+        s2 += sum_vec16<TIn, Acc>(c);
+        s3 += sum_vec16<TIn, Acc>(d);
+    }
+    for (; i < nvec; i += stride) s0 += sum_vec16<TIn, Acc>(ld_stream(v + i));
+    for (int64_t j = nvec * PER + tid; j < n; j += stride) s1 += to_acc<Acc, TIn>(in[j]);
+    Acc s = (s0 + s1) + (s2 + s3);
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
     if ((threadIdx.x & 31) == 0) sh[threadIdx.x >> 5] = s;
@@ -653,25 +692,45 @@ __global__ void __launch_bounds__(1024) sum_final_kernel(const Acc *partials, in
     }
 }
 
+// Exclusive offset of shard `index` from the gathered per-shard totals: totals[0] + ... + totals[index-1] in the
+// scan's own arithmetic (unsigned wrap / float32 or int64 adds in shard order).  One thread; it exists so that
+// the multi-GPU scan never leaves the stream between its two passes.
+template <typename Acc>
+__global__ void scan_offset_kernel(const Acc *totals, int index, Acc *out) {
+    Acc s = 0;
+    for (int i = 0; i < index; ++i) s += totals[i];
+    *out = s;
+}
+
 // ---- scratch -------------------------------------------------------------------------------
 // One buffer per (device, stream): launches on one stream are ordered, so they can share it, and
 // launches on different streams never collide.  A stream that is being captured into a CUDA graph
 // cannot allocate, and the graph may later be replayed on any stream, so captured launches use one
 // extra per-device buffer that every ordinary call keeps at least as large as its own (run the
-// same call once before capturing it).
-struct Scratch { void *ptr = nullptr; size_t bytes = 0; };
+// same call once before capturing it).  A graph keeps the address it captured in its memset node and
+// kernel arguments, so a capture buffer that was ever handed out under capture is never freed or moved:
+// when a later ordinary call needs a larger one, the old block is retired (kept until exit) and new
+// captures get the larger block.  All captured scans of a device share their block: replay two such
+// graphs on different streams at the same time and their descriptors race.
+struct Scratch { void *ptr = nullptr; size_t bytes = 0; bool captured = false; };
 std::mutex g_scratch_mu;
 std::map<std::pair<int, void *>, Scratch> g_scratch;
+std::vector<void *> g_retired;  // capture buffers that instantiated graphs may still point at
 void *const kCaptureKey = reinterpret_cast<void *>(~uintptr_t(0));
 
 bool grow(Scratch &s, size_t bytes, cudaStream_t st) {
     if (s.bytes >= bytes) return true;
     if (s.ptr) {
-        cudaStreamSynchronize(st);  // earlier launches may still use it
-        cudaFree(s.ptr);
+        if (s.captured) {
+            g_retired.push_back(s.ptr);
+        } else {
+            cudaStreamSynchronize(st);  // earlier launches may still use it
+            cudaFree(s.ptr);
+        }
     }
     s.ptr = nullptr;
     s.bytes = 0;
+    s.captured = false;
     const size_t want = bytes < (1u << 20) ? (1u << 20) : bytes;
     if (cudaMalloc(&s.ptr, want) != cudaSuccess) {
         cudaGetLastError();
@@ -690,7 +749,9 @@ void *scratch_get(size_t bytes, void *stream) {
     std::lock_guard<std::mutex> lock(g_scratch_mu);
     if (cap != cudaStreamCaptureStatusNone) {
         Scratch &c = g_scratch[{dev, kCaptureKey}];
-        return c.bytes >= bytes ? c.ptr : nullptr;
+        if (c.bytes < bytes) return nullptr;
+        c.captured = true;
+        return c.ptr;
     }
     if (!grow(g_scratch[{dev, kCaptureKey}], bytes, nullptr)) return nullptr;
     Scratch &s = g_scratch[{dev, stream}];
@@ -799,7 +860,7 @@ int launch_sum(const void *in, void *total, int64_t n, void *stream) {
     using Acc = typename AccOf<TIn>::type;
     cudaStream_t st = as_stream(stream);
     int64_t grid = (int64_t)device_props().sm_count * 8;
-    const int64_t need = cdiv(n > 0 ? n : 1, 256 * 8);
+    const int64_t need = cdiv(n > 0 ? n : 1, 256 * 4 * (16 / (int64_t)sizeof(TIn)));
     if (grid > need) grid = need;
     Acc *partials = (Acc *)scratch_get((size_t)grid * sizeof(Acc), stream);
     if (!partials) return fail(ENC_ERR_NO_MEMORY, "enc_sum: cannot allocate scratch");
@@ -880,6 +941,8 @@ void scratch_release_all() {
     for (auto &kv : g_scratch)
         if (kv.second.ptr) cudaFree(kv.second.ptr);
     g_scratch.clear();
+    for (void *p : g_retired) cudaFree(p);
+    g_retired.clear();
 }
 
 }  // namespace enc
@@ -927,6 +990,25 @@ extern "C" int enc_sum(const void *in, void *total, int64_t n, int dtype, void *
         case ENC_I64: return enc::launch_sum<long long>(in, total, n, stream);
         default: return enc::fail(ENC_ERR_BAD_ARG, "enc_sum: unsupported dtype %d", dtype);
     }
+}
+
+extern "C" int enc_scan_offset(const void *totals, int count, int index, void *offset, int dtype, void *stream) {
+    ENC_PROLOGUE();
+    if (!totals || !offset || count < 0 || index < 0 || index > count) return enc::fail(ENC_ERR_BAD_ARG, "enc_scan_offset: bad argument (count %d, index %d)", count, index);
+    cudaStream_t st = enc::as_stream(stream);
+    switch (dtype) {
+        case ENC_F32: case ENC_F16: case ENC_BF16:
+            enc::scan_offset_kernel<float><<<1, 1, 0, st>>>((const float *)totals, index, (float *)offset);
+            break;
+        case ENC_I32: case ENC_I8: case ENC_U8: case ENC_I16:
+            enc::scan_offset_kernel<unsigned><<<1, 1, 0, st>>>((const unsigned *)totals, index, (unsigned *)offset);
+            break;
+        case ENC_I64:
+            enc::scan_offset_kernel<unsigned long long><<<1, 1, 0, st>>>((const unsigned long long *)totals, index, (unsigned long long *)offset);
+            break;
+        default: return enc::fail(ENC_ERR_BAD_ARG, "enc_scan_offset: unsupported dtype %d", dtype);
+    }
+    return enc::check_launch("enc_scan_offset");
 }
 
 // Flat inclusive scan for callers that are not allowed to allocate device memory (see above).  Nothing

@@ -3,12 +3,13 @@
 // All three are HBM-bound: one read and one write of the matrix.  A row is loaded ONCE with
 // 128-bit streaming loads into registers (up to 32 float values per thread), reduced with warp
 // shuffles plus one shared-memory exchange when a row spans several warps, and written back with
-// 128-bit stores.  Statistics are float32; the LayerNorm variance is the centred second pass
-// computed from the registers, so nothing is re-read.  Rows wider than the register budget take a
-// three-pass kernel that re-reads the row through L2.
+// 128-bit stores.  Statistics are float32; the LayerNorm variance comes from one pass over the registers
+// (sum and sum of squares), with the reference's centred second pass, again from the registers, for rows
+// whose mean is large against their spread, so nothing is re-read.  Rows wider than the register budget
+// take a three-pass kernel that re-reads the row through L2.
 //
 // The formulas are the reference kernels' (examples/02_softmax.py:15-24, examples/03_layernorm.py:15-42,
-// examples/06_rmsnorm.py:15-24): max-subtracted softmax, two-pass centred variance, 1/sqrt(var+eps).
+// examples/06_rmsnorm.py:15-24): max-subtracted softmax, biased variance, 1/sqrt(var+eps).
 // At B200's ratio of HBM bandwidth to FP32 issue rate a bf16 element has a budget of about twenty
 // lane-instructions, so the per-element work is kept short: fused multiply-adds where the reference
 // rounds twice, exp as ex2.approx of a pre-scaled argument, one reciprocal per row instead of a
@@ -38,12 +39,9 @@ struct RowArgs {
 };
 
 enum { OP_SOFTMAX = 0, OP_LAYERNORM = 1, OP_RMSNORM = 2 };
-#ifndef ENC_ROW_PACKED
-#define ENC_ROW_PACKED 6
-#endif
 // Packed f32x2 instructions, as a bit mask: 1 = LayerNorm sums, 2 = LayerNorm output, 4 = RMSNorm (both passes).
 // Measured at bf16 [16384, 4096]: 2 and 4 gain 1-2%, 1 loses 3% (the pair moves cost more than the adds save).
-constexpr int ROW_PACKED_MASK = ENC_ROW_PACKED;
+constexpr int ROW_PACKED_MASK = 2 | 4;
 
 // Reduction over the `tpr` threads that share a row.  `slot` is a per-call shared array so that
 // consecutive reductions need one barrier each.

@@ -69,13 +69,24 @@ def sharded_histogram(x_local: Any, num_bins: int, lo: float, hi: float, local_h
     return allreduce_histogram(local_histogram(x_local, num_bins, lo, hi), group)
 
 
+def host_offset(gathered: Any, rank: int) -> Any:
+    """Exclusive offset of `rank` from the gathered totals, computed on the host (CPU ranks over gloo)."""
+    import torch
+
+    offs = exclusive_offsets(gathered.cpu().numpy())
+    return torch.from_numpy(offs[rank : rank + 1].copy()).to(gathered.device)
+
+
 def sharded_cumsum(x_local: Any, local_total: Callable[[Any], Any], local_scan: Callable[[Any, Any], Any],
-                   group: Any = None) -> Any:
+                   group: Any = None, offset: Callable[[Any, int], Any] | None = None) -> Any:
     """Inclusive scan of one flat array split contiguously across ranks (rank r holds shard r).
 
     `local_total(x_local)` returns a one-element torch tensor (accumulator dtype) with the shard's sum;
     `local_scan(x_local, seed)` returns the shard's inclusive scan with `seed` (a one-element tensor,
-    the exclusive offset) added.  Traffic per rank: the shard is read twice and written once.
+    the exclusive offset) added; `offset(gathered, rank)` turns the all-gathered totals into that seed
+    (default: `cuda_offset` for CUDA tensors, which is a one-thread kernel on the launch stream, so the
+    two passes and the all-gather between them stay stream-ordered with no host round trip; `host_offset`
+    otherwise).  Traffic per rank: the shard is read twice and written once.
     """
     import torch
     import torch.distributed as dist
@@ -86,10 +97,9 @@ def sharded_cumsum(x_local: Any, local_total: Callable[[Any], Any], local_scan: 
     world, rank = dist.get_world_size(group), dist.get_rank(group)
     gathered = torch.empty(world, dtype=total.dtype, device=total.device)
     dist.all_gather_into_tensor(gathered, total.reshape(1), group=group)
-    host = gathered.cpu().numpy()
-    offs = exclusive_offsets(host)
-    seed = torch.from_numpy(offs[rank : rank + 1].copy()).to(total.device)
-    return local_scan(x_local, seed)
+    if offset is None:
+        offset = cuda_offset if gathered.is_cuda else host_offset
+    return local_scan(x_local, offset(gathered, rank))
 
 
 # ---- CUDA-backed local steps -------------------------------------------------------------------
@@ -104,6 +114,20 @@ def cuda_total(x: Any) -> Any:
     acc = torch.float32 if code in (N.F32, N.F16, N.BF16) else (torch.int64 if code == N.I64 else torch.int32)
     out = torch.empty(1, dtype=acc, device=x.device)
     N.call("enc_sum", x.data_ptr(), out.data_ptr(), x.numel(), code, interop.current_stream())
+    return out
+
+
+def cuda_offset(gathered: Any, rank: int) -> Any:
+    """Exclusive offset of `rank` from the gathered totals, on the device and on the current stream."""
+    import torch
+
+    from enceladus_b200 import _native as N
+    from enceladus_b200.runtime import interop
+
+    code = {torch.float32: N.F32, torch.int32: N.I32, torch.int64: N.I64}[gathered.dtype]
+    out = torch.empty(1, dtype=gathered.dtype, device=gathered.device)
+    N.call("enc_scan_offset", gathered.data_ptr(), gathered.numel(), int(rank), out.data_ptr(), code,
+           interop.current_stream())
     return out
 
 

@@ -14,9 +14,13 @@ interpreter and no CPU fallback in this build.
 
 from __future__ import annotations
 
+import ast
 import functools
+import hashlib
 import inspect
 import os
+import textwrap
+import warnings
 from collections.abc import Callable, Iterable, Mapping
 from dataclasses import dataclass
 from typing import Any
@@ -59,6 +63,51 @@ def resolve_grid(grid: Any, bound: Mapping[str, Any]) -> tuple[int, int, int]:
         if x > lim:
             raise ValueError(f"grid dimension {i} is {x}, but the limit is {lim}")
     return g  # type: ignore[return-value]
+
+
+def fingerprint_of_def(node: ast.FunctionDef) -> str | None:
+    """SHA-256 of a function's normalised body, or None when the body only documents the kernel (a docstring,
+    `pass`, `...`).  Normalised = the AST of the statements without the docstring and without positions, so
+    comments, blank lines and line breaks do not change it; names and constants do."""
+    body = list(node.body)
+    if body and isinstance(body[0], ast.Expr) and isinstance(getattr(body[0], "value", None), ast.Constant) \
+            and isinstance(body[0].value.value, str):
+        body = body[1:]
+    body = [b for b in body if not isinstance(b, ast.Pass)
+            and not (isinstance(b, ast.Expr) and isinstance(b.value, ast.Constant) and b.value.value is Ellipsis)]
+    if not body:
+        return None
+    text = "\n".join(ast.dump(b, annotate_fields=True, include_attributes=False) for b in body)
+    return hashlib.sha256(text.encode()).hexdigest()
+
+
+def body_fingerprint(fn: Callable[..., Any]) -> str | None:
+    """`fingerprint_of_def` of a live function; raises OSError when its source cannot be read."""
+    tree = ast.parse(textwrap.dedent(inspect.getsource(fn)))
+    node = next(n for n in ast.walk(tree) if isinstance(n, (ast.FunctionDef, ast.AsyncFunctionDef)))
+    return fingerprint_of_def(node)
+
+
+def check_body(fn: Callable[..., Any], name: str) -> None:
+    """A `@jit` definition is served by the hand-written kernel registered under its name.  That is only right
+    if the body says the same thing: either nothing (docstring / `pass`) or exactly one of the reference's own
+    kernels of that name.  Anything else is refused: the reference would have compiled what the user wrote."""
+    try:
+        fp = body_fingerprint(fn)
+    except (OSError, TypeError, SyntaxError, StopIteration):
+        warnings.warn(f"kernel `{name}`: the source of this definition cannot be read, so its body cannot be "
+                      "compared with the built-in CUDA kernel that will run in its place", RuntimeWarning, stacklevel=4)
+        return
+    if fp is None:
+        return
+    from enceladus_b200.runtime.kernel_bodies import KNOWN_BODIES
+
+    if fp not in KNOWN_BODIES.get(name, ()):
+        raise NotImplementedError(
+            f"kernel `{name}` has a body that is not the reference's kernel of that name. This build does not "
+            "compile kernel bodies: a launch of this name runs the hand-written CUDA kernel, which would ignore "
+            "what the body says. Rename the kernel if it computes something else, or leave the body empty "
+            "(a docstring or `pass`) to use the built-in kernel.")
 
 
 @dataclass
@@ -132,11 +181,15 @@ class JITFunction:
         return dict(ba.arguments)
 
     def adapter(self):
-        """The registry entry that implements this kernel; raises if there is none."""
+        """The registry entry that implements this kernel; raises if there is none, or if this definition's
+        body is code that is not the reference's kernel of that name (the body is never executed, so serving
+        it with the built-in kernel would silently compute something else)."""
         if self._adapter is None:
             from enceladus_b200.runtime import registry
 
-            self._adapter = registry.lookup(self.__name__, tuple(self.arg_names))
+            ad = registry.lookup(self.__name__, tuple(self.arg_names))
+            check_body(self.fn, ad.name)
+            self._adapter = ad
         return self._adapter
 
     def run(self, *args: Any, grid: Any, num_warps: int = 4, num_stages: int | None = None,
@@ -268,7 +321,11 @@ def launch(ad, bound: dict[str, Any], grid: tuple[int, int, int], variant: int, 
                 raise TypeError(f"argument `{name}` is a torch tensor on {v.device}; pass a CUDA tensor "
                                 "or a NumPy array")
             if dev is None:
-                dev = v.device
+                dev, dev_name = v.device, name
+            elif v.device != dev:
+                # a pointer into another GPU's memory would reach the kernel as a peer (or foreign) address
+                raise ValueError(f"argument `{name}` lives on {v.device} but `{dev_name}` lives on {dev}; "
+                                 "all array arguments of one launch must be on the same device")
         elif isinstance(v, np.ndarray):
             host_names = [name] if host_names is None else [*host_names, name]
         else:

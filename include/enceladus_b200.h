@@ -12,8 +12,10 @@
  *
  *   - plain pointers and sizes only; every pointer is a DEVICE pointer on the current CUDA device
  *     unless the parameter name ends in `_host`;
- *   - the caller owns all buffers; the library allocates nothing except one cached per-device
- *     scratch buffer used by enc_cumsum (tile descriptors) — see enc_cumsum;
+ *   - the caller owns all buffers.  The library itself owns, per device: a 256-byte status block (bounded
+ *     device-side waits report there), the tile-descriptor scratch of enc_cumsum / enc_sum (see enc_cumsum)
+ *     and a workspace for split-K partial sums of enc_matmul (see enc_matmul); all are allocated on first
+ *     use and freed at exit;
  *   - `stream` is a cudaStream_t / CUstream passed as void* (NULL = the legacy default stream); work
  *     is enqueued and the call returns without synchronising, like fr_stream_dispatch;
  *   - the return value is an enc_status; on failure enc_last_error() holds a message for the calling
@@ -105,7 +107,8 @@ int enc_synchronize(void *stream);
 int enc_softmax(const void *in, void *out, int64_t rows, int64_t cols, int64_t stride_in,
                 int64_t stride_out, int dtype, int variant, void *stream);
 
-/* LayerNorm forward: y = (x-mean)*rstd*w + b, mean/rstd float32 per row (two-pass centred variance).
+/* LayerNorm forward: y = (x-mean)*rstd*w + b, mean/rstd float32 per row (biased variance: one pass of sum and
+ * sum of squares, the centred second pass of the reference for rows with mean^2 > 16 var).
  * Replaces layernorm_kernel[(rows,)](x, y, w, b, mean, rstd, stride_x, stride_y, n_cols, eps, BLOCK)
  *                                                                                    examples/03_layernorm.py:15-57
  * x, y, w, b share `dtype`.  mean / rstd may be NULL (not written). */
@@ -162,8 +165,10 @@ int enc_cumsum_out_dtype(int dtype);
  * refused with ENC_ERR_UNSUPPORTED.  The first call on a device resolves the array's device address;
  * make that call before any stream capture.  Every call on a device shares the array: calls on one
  * stream are safe, calls that overlap on the GPU race.  `status` (device pointer owned by the caller, or
- * NULL) is set non-zero if a bounded device-side wait ran out.  Same dtypes and results as enc_cumsum
- * except ENC_I64. */
+ * NULL) is set non-zero if a bounded device-side wait ran out, in which case the output is invalid.  With
+ * status == NULL that timeout is recorded only in a spare word of the array that nothing reads, so the
+ * failure is SILENT (enc_synchronize does not report it either): pass a status word unless a wrong output
+ * would be caught downstream.  Same dtypes and results as enc_cumsum except ENC_I64. */
 int enc_cumsum_noalloc(const void *in, void *out, int64_t n, int dtype, const void *seed,
                        unsigned *status, void *stream);
 
@@ -171,6 +176,13 @@ int enc_cumsum_noalloc(const void *in, void *out, int64_t n, int dtype, const vo
  * Pass 1 of the multi-GPU flat scan (local total -> all-gather -> seed).  No counterpart in the
  * reference, which has no multi-device path. */
 int enc_sum(const void *in, void *total, int64_t n, int dtype, void *stream);
+
+/* offset[0] = totals[0] + ... + totals[index-1] (0 for index 0) in the accumulator type of enc_cumsum for
+ * `dtype` (32-bit wrap, float32 or int64 adds in shard order): the `seed` of shard `index` once the per-shard
+ * totals of enc_sum have been all-gathered into `totals` (device, `count` values).  A one-thread kernel on
+ * `stream`, so that the two passes of the multi-GPU scan and the collective between them stay stream-ordered
+ * with no host round trip.  No counterpart in the reference (single device). */
+int enc_scan_offset(const void *totals, int count, int index, void *offset, int dtype, void *stream);
 
 /* ---- tensor-core kernels ------------------------------------------------------------------ */
 
@@ -200,7 +212,10 @@ int enc_matmul_int(const void *a, const void *b, void *c, int64_t M, int64_t N, 
  * O = softmax(Q K^T * sm_scale [causal]) V, base-2 online softmax in float32, P rounded to the input
  * dtype before P@V, O in the input dtype.  lse (float32 [bh, seq], may be NULL) receives
  * ln2*(m + log2 l) of the running statistics.  stride_h = elements between slices, stride_m =
- * elements between rows (head_dim contiguous).  dtype: ENC_F16 | ENC_BF16; head_dim 64 or 128.
+ * elements between rows (head_dim contiguous).  dtype: ENC_F16 | ENC_BF16 | ENC_F32; head_dim <= 128.
+ * float16 / bfloat16 with head_dim 64 or 128, 16-byte aligned tensors and strides that are multiples of 8
+ * run on the tcgen05 tensor cores; every other accepted shape runs on a CUDA-core kernel with the same
+ * arithmetic.
  * Replaces attention_kernel[(cdiv(S,BLOCK_M), B*H)](q, k, v, o, sm_scale, N_CTX, stride_h, stride_m, HEAD_DIM, ...)
  *                                                                                    examples/08_flash_attention.py:30-103 */
 int enc_attention_fwd(const void *q, const void *k, const void *v, void *o, float *lse, int64_t bh,

@@ -310,11 +310,73 @@ def test_sharded_flat_cumsum_matches_single_pass(oracle):
     x = np.random.default_rng(11).integers(0, 1 << 29, n).astype(np.int32)
     want = oracle.cumsum(x)
     shards = [torch_of(x[slice(*edist.shard_range(n, r, world, 4))]) for r in range(world)]
-    totals = np.concatenate([host(edist.cuda_total(s)) for s in shards])
-    offs = edist.exclusive_offsets(totals)
-    got = np.concatenate([host(edist.cuda_scan(s, torch.from_numpy(offs[r : r + 1].copy()).cuda()))
-                          for r, s in enumerate(shards)])
+    gathered = torch.cat([edist.cuda_total(s) for s in shards])  # what the all-gather leaves on every rank
+    offs = edist.exclusive_offsets(host(gathered))
+    seeds = [edist.cuda_offset(gathered, r) for r in range(world)]  # one-thread kernel, stays on the stream
+    np.testing.assert_array_equal(np.concatenate([host(t) for t in seeds]), offs)
+    got = np.concatenate([host(edist.cuda_scan(s, seeds[r])) for r, s in enumerate(shards)])
     np.testing.assert_array_equal(got, want)
+    # float32 totals are added in shard order, as the host rule does
+    f = torch.tensor([0.1, 0.2, 0.3, 1e8], device="cuda")
+    np.testing.assert_array_equal(np.concatenate([host(edist.cuda_offset(f, r)) for r in range(4)]),
+                                  edist.exclusive_offsets(host(f)))
+
+
+def test_enc_sum_matches_the_wrapped_total_for_every_dtype_and_alignment(oracle):
+    import torch
+
+    r = np.random.default_rng(14)
+    for dt, lo, hi in ((np.int32, 0, 1 << 30), (np.int8, -128, 128), (np.uint8, 0, 256), (np.int16, -30000, 30000)):
+        for n, off in ((1, 0), (1_000_003, 0), (70_001, 1), ((1 << 22) + 5, 3)):
+            x = r.integers(lo, hi, n + off).astype(dt)
+            xt = torch_of(x)[off:]  # off > 0: not 16-byte aligned, scalar path
+            want = x[off:].astype(np.int64).sum() & 0xFFFFFFFF
+            assert int(host(edist_total(xt))[0]) & 0xFFFFFFFF == want, (dt, n, off)
+    xf = r.standard_normal(3_000_001).astype(np.float32)
+    got = float(host(edist_total(torch_of(xf)))[0])
+    assert abs(got - xf.astype(np.float64).sum()) <= 1e-3 * np.abs(xf).sum() ** 0.5 + 1e-2
+
+
+def edist_total(t):
+    from enceladus_b200 import dist as edist
+
+    return edist.cuda_total(t)
+
+
+def test_captured_scan_survives_a_larger_eager_scan(oracle):
+    """A CUDA graph keeps the address of the scan's descriptor buffer.  A later eager scan that needs a larger
+    buffer must not free or move the captured one: replaying the graph afterwards gives the same result."""
+    import torch
+
+    n_small = 300_007
+    x = torch_of(np.random.default_rng(15).integers(0, 1 << 28, n_small).astype(np.int32))
+    out = torch.empty_like(x)
+
+    def scan():
+        ops.cumsum_kernel[(1,)](out, x, 1, n_small, n_small, n_small, REVERSE=False, BLOCK_M=1, BLOCK_N=1 << 19)
+
+    scan()  # sizes the per-device capture buffer; nothing can be allocated during capture
+    torch.cuda.synchronize()
+    want = oracle.cumsum(host(x))
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        scan()
+    g.replay()
+    torch.cuda.synchronize()
+    np.testing.assert_array_equal(host(out), want)
+    # 6e8 int8 values -> 146k tiles of 4096 -> more than the 1 MiB of descriptors the buffer starts with
+    n_big = 600_000_000
+    big = torch.randint(0, 100, (n_big,), device="cuda", dtype=torch.int8)
+    big_out = torch.empty(n_big, device="cuda", dtype=torch.int32)
+    ops.cumsum_kernel[(1,)](big_out, big, 1, n_big, n_big, n_big, REVERSE=False, BLOCK_M=1, BLOCK_N=1 << 30)
+    torch.cuda.synchronize()
+    assert (int(big_out[-1]) & 0xFFFFFFFF) == (int(big.sum(dtype=torch.int64)) & 0xFFFFFFFF)
+    del big, big_out
+    out.zero_()
+    g.replay()
+    torch.cuda.synchronize()
+    np.testing.assert_array_equal(host(out), want)
+    enceladus.synchronize()
 
 
 # ---- launch path -----------------------------------------------------------------------------------

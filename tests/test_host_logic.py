@@ -388,3 +388,72 @@ def test_piecewise_staging_plan_covers_every_unit_once_on_aligned_boundaries(mon
     assert jit._pipeline_plan(ad, bound, (m, 1, 1), hosts) is None
     # kernels without independent pieces have no split at all
     assert ops.histogram_kernel.adapter().split is None
+
+
+def test_same_name_kernel_with_another_body_is_refused():
+    """The body of a `@jit` kernel is never executed: a definition whose code is not the reference's kernel of
+    that name must not be served by the built-in kernel."""
+    @enceladus.jit
+    def add_kernel(x_ptr, y_ptr, out_ptr, n, BLOCK: tl.constexpr):
+        offs = tl.program_id(0) * BLOCK + tl.arange(0, BLOCK)
+        mask = offs < n
+        tl.store(out_ptr + offs, tl.load(x_ptr + offs, mask=mask) - tl.load(y_ptr + offs, mask=mask), mask=mask)
+
+    x = np.zeros(8, np.float32)
+    with pytest.raises(NotImplementedError, match="not the reference's kernel of that name"):
+        add_kernel[(1,)](x, x, x, 8, BLOCK=8)
+
+    # the reference's own body (examples/01_vector_add.py:15-22) is accepted, however it is formatted
+    @enceladus.jit
+    def add_kernel(x_ptr, y_ptr, out_ptr, n, BLOCK: tl.constexpr):  # noqa: F811
+        offs = tl.program_id(0) * BLOCK + tl.arange(0, BLOCK)
+        mask = offs < n  # a comment does not change the fingerprint
+
+        tl.store(out_ptr + offs, tl.load(x_ptr + offs, mask=mask) + tl.load(y_ptr + offs, mask=mask), mask=mask)
+
+    assert add_kernel.adapter().name == "add_kernel"
+
+    @enceladus.jit
+    def add_kernel(x_ptr, y_ptr, out_ptr, n, BLOCK: tl.constexpr):  # noqa: F811
+        """Documentation only."""
+        ...
+
+    assert add_kernel.adapter().name == "add_kernel"
+    from enceladus_b200 import ops
+
+    for name in registry.kernels():  # every kernel the package itself defines resolves
+        k = getattr(ops, name, None)
+        if k is not None and hasattr(k, "adapter"):
+            assert k.adapter().name == name
+
+
+def test_tensors_on_two_devices_are_refused(monkeypatch):
+    """All array arguments of a launch must live on one device; checked before anything reaches the library."""
+    from enceladus_b200.runtime import interop, jit
+
+    class FakeDevice:
+        def __init__(self, index):
+            self.index = index
+
+        def __eq__(self, other):
+            return self.index == other.index
+
+        def __ne__(self, other):
+            return self.index != other.index
+
+        def __repr__(self):
+            return f"cuda:{self.index}"
+
+    class FakeTensor:
+        is_cuda = True
+
+        def __init__(self, index):
+            self.device = FakeDevice(index)
+
+    monkeypatch.setattr(interop, "tensor_type", lambda: FakeTensor)
+    from enceladus_b200 import ops
+
+    ad = ops.add_kernel.adapter()
+    bound = {"x_ptr": FakeTensor(0), "y_ptr": FakeTensor(0), "out_ptr": FakeTensor(1), "n": 4, "BLOCK": 4}
+    with pytest.raises(ValueError, match=r"`out_ptr` lives on cuda:1 but `x_ptr` lives on cuda:0"):
+        jit.launch(ad, bound, (1, 1, 1), -1, None)

@@ -9,6 +9,8 @@ purpose: if it fails under `-x`, every other test has already run.
 Both entry points are called through the C ABI (ctypes) on raw device pointers; the result of the new one
 must equal the existing one's (integers bit for bit, float32 within the tolerance the other scan tests
 use), on two calls in a row, because the array keeps the previous call's contents and must be cleared.
+The integer results are also held to the oracle (np.cumsum in int32, wrapping modulo 2^32), so that the
+two entry points cannot agree on a wrong answer.
 """
 
 from __future__ import annotations
@@ -39,7 +41,7 @@ def _scan_both(x):
     return ref, got, int(status.item())
 
 
-def test_noalloc_scan_matches_the_allocating_entry_point_twice_in_a_row():
+def test_noalloc_scan_matches_the_allocating_entry_point_twice_in_a_row(oracle):
     import torch
 
     g = torch.Generator(device="cuda").manual_seed(0)
@@ -50,6 +52,7 @@ def test_noalloc_scan_matches_the_allocating_entry_point_twice_in_a_row():
         ref, got, status = _scan_both(x)
         assert status == 0
         assert torch.equal(ref, got)
+        np.testing.assert_array_equal(got.cpu().numpy(), oracle.cumsum(x.cpu().numpy()))
     for n in (3_000_001, 70_000):
         x = torch.randn(n, device="cuda", generator=g)
         ref, got, status = _scan_both(x)
@@ -61,7 +64,7 @@ def test_noalloc_scan_matches_the_allocating_entry_point_twice_in_a_row():
         assert np.abs(got.cpu().numpy() - ref.cpu().numpy()).max() <= 1e-4 * scale
 
 
-def test_noalloc_scan_takes_a_seed_and_refuses_what_does_not_fit():
+def test_noalloc_scan_takes_a_seed_and_refuses_what_does_not_fit(oracle):
     import torch
 
     lib = N.load()
@@ -73,6 +76,12 @@ def test_noalloc_scan_takes_a_seed_and_refuses_what_does_not_fit():
     torch.cuda.synchronize()
     want = torch.cumsum(x.to(torch.int64), 0) + 41
     assert torch.equal(out.to(torch.int64), want)
+    # a seed that makes the very first output wrap: (2^31 - 1) + x[0] + ... in uint32 arithmetic
+    seed = torch.tensor([2**31 - 1], device="cuda", dtype=torch.int32)
+    N.check(lib.enc_cumsum_noalloc(x.data_ptr(), out.data_ptr(), x.numel(), N.I32, seed.data_ptr(), None, stream))
+    torch.cuda.synchronize()
+    want = (oracle.cumsum(x.cpu().numpy()).view(np.uint32) + np.uint32(2**31 - 1)).view(np.int32)
+    np.testing.assert_array_equal(out.cpu().numpy(), want)
     too_long = (1 << 30) + 1  # refused before anything is touched, so the pointers are never read
     rc = lib.enc_cumsum_noalloc(ctypes.c_void_p(256), ctypes.c_void_p(256), too_long, N.I32, None, None, stream)
     assert rc == N.ERR_UNSUPPORTED and "exceed" in N.last_error()
