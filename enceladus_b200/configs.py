@@ -20,7 +20,7 @@ _HALF_NAMES = ("float16", "fp16", "f16", "half", "bfloat16", "bf16")
 # (BM, BN, BK, stages) of the tcgen05 matmul variants, in the order the native library numbers them.
 MATMUL_TILES = [(128, 256, 64, 4), (128, 128, 64, 6), (128, 256, 64, 3), (128, 64, 64, 8)]
 # (BLOCK_M, BLOCK_N) of the attention variants.
-ATTENTION_TILES = [(256, 128), (128, 128), (128, 128), (256, 64)]
+ATTENTION_TILES = [(256, 128), (128, 128), (128, 128), (256, 64), (256, 64)]
 
 
 def _dtype_name(dtype: Any) -> str:

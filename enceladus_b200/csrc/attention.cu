@@ -945,6 +945,372 @@ attention_ts64_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
     }
 }
 
+// ---- persistent form of the 64-key-block kernel ---------------------------------------------------------------
+// The kernel above pays, per 256 query rows, for a CTA launch, barrier set-up, a TMEM allocation, the first Q / K
+// loads with nothing to overlap them, and an epilogue during which the tensor core has nothing queued: measured
+// from the full and the causal timings at [8, 32, 4096, 128], about 8 microseconds per CTA against 66 (full) or
+// 40 (causal) in total.  Here one CTA per SM walks a static list of work items (256 query rows of one (batch,
+// head) slice each); barriers and tensor memory are set up once, every ring and every barrier phase simply keeps
+// counting across items, and the roles run ahead of each other as far as the data allows:
+//   producer       loads the next item's Q tiles as soon as the score products of the current item have read them
+//                  (q_empty, committed behind the last score MMA) and keeps the K / V rings full across the seam;
+//   score issuers  issue S(0), S(1) of the next item while the softmax warps are still in the epilogue;
+//   P V issuer     starts the next item's accumulation once the softmax warps have pulled O out of tensor memory
+//                  (o_empty); o_full is per tile, so with a causal mask the upper tile's epilogue overlaps the
+//                  lower tile's last two key blocks.
+// Schedule: item k = (slice k / n_qb, query block perm[k % n_qb]); CTA c takes k = r G + c in even rounds r and
+// k = r G + (G-1-c) in odd ones.  Consecutive items share a slice, so the CTAs of a round read a few slices' K / V
+// from L2 as the one-shot grid does.  For causal launches `perm` pairs the query blocks so that the two items a
+// CTA gets in an even/odd pair of rounds have a constant total number of key blocks (the host builds it from
+// (G, n_qb); see balance_perm): 98.8% balance for 4096 items on 148 SMs, with no work counter in global memory.
+struct PersistArgs {
+    AttnArgs a;
+    int n_qb;      // query blocks of 256 rows per slice
+    int n_items;   // n_qb * slices
+    uint8_t perm[64];  // query-block order inside a slice (identity beyond 64 blocks)
+};
+
+struct ItemIter {
+    int G, c, n_items, n_qb, r;
+    const uint8_t *perm;
+    __device__ ItemIter(const PersistArgs &p) : G((int)gridDim.x), c((int)blockIdx.x), n_items(p.n_items), n_qb(p.n_qb), r(0), perm(p.perm) {}
+    // next item of this CTA: false when there is none left
+    __device__ bool next(int &bh, int &qb) {
+        for (;; ++r) {
+            const long long base = (long long)r * G;
+            if (base >= n_items) return false;
+            const long long k = base + ((r & 1) ? G - 1 - c : c);
+            if (k >= n_items) continue;
+            bh = (int)(k / n_qb);
+            const int q = (int)(k % n_qb);
+            qb = n_qb <= 64 ? perm[q] : q;
+            ++r;
+            return true;
+        }
+    }
+};
+
+// key blocks of 64 the two tiles of query block qb need
+__device__ __forceinline__ void item_extent(const AttnArgs &a, int qb, int64_t &m0, int (&nkv_t)[2], int &nkv) {
+    m0 = (int64_t)qb * (2 * BM);
+#pragma unroll
+    for (int t = 0; t < 2; ++t) {
+        const int64_t r0 = m0 + t * BM;
+        const int64_t hi = a.causal ? (r0 + BM < a.seq ? r0 + BM : a.seq) : a.seq;
+        nkv_t[t] = r0 < a.seq ? (int)((hi + BN64 - 1) / BN64) : 0;
+    }
+    nkv = nkv_t[0] > nkv_t[1] ? nkv_t[0] : nkv_t[1];
+}
+
+template <int D, int STAGES> struct AttnSmemP {  // like AttnSmem64, with per-tile Q and O barriers
+    static constexpr int QTILE = BM * D * 2;
+    static constexpr int TILE = BN64 * D * 2;
+    static constexpr int Q_OFF = 0;
+    static constexpr int K_OFF = 2 * QTILE;
+    static constexpr int V_OFF = K_OFF + STAGES * TILE;
+    static constexpr int BAR_OFF = V_OFF + STAGES * TILE;
+    static constexpr int NBARS = 4 + 4 * STAGES + 12 + 4;  // q full/empty x2, k/v full/empty, (s_full, p_full, pv_done) x4, o full/empty x2
+    static constexpr int TOTAL = BAR_OFF + NBARS * 8 + 16;
+};
+
+template <typename T, int D, int STAGES>
+__global__ void __launch_bounds__(kThreads2, 1)
+attention_p64_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
+                     const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ PersistArgs pa) {
+    using L = AttnSmemP<D, STAGES>;
+    constexpr int BNK = BN64;
+    const AttnArgs &a = pa.a;
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
+    uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint64_t *q_full = reinterpret_cast<uint64_t *>(smem + L::BAR_OFF);  // [2]
+    uint64_t *q_empty = q_full + 2;                                      // [2]
+    uint64_t *k_full = q_empty + 2;
+    uint64_t *k_empty = k_full + STAGES;
+    uint64_t *v_full = k_empty + STAGES;
+    uint64_t *v_empty = v_full + STAGES;
+    uint64_t *s_full = v_empty + STAGES;  // [tile * 2 + buffer]
+    uint64_t *p_full = s_full + 4;
+    uint64_t *pv_done = p_full + 4;
+    uint64_t *o_full = pv_done + 4;       // [2]
+    uint64_t *o_empty = o_full + 2;       // [2]
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(o_empty + 2);
+    volatile uint32_t *abort = tmem_slot + 1;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    constexpr uint32_t TMEM_COLS = 512;
+
+    if (threadIdx.x == 0) {
+        for (int t = 0; t < 2; ++t) {
+            mbar_init(&q_full[t], 1);
+            mbar_init(&q_empty[t], 1);
+            mbar_init(&o_full[t], 1);
+            mbar_init(&o_empty[t], 128);
+        }
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(&k_full[s], 1);
+            mbar_init(&k_empty[s], 2);  // the score issuers of both tiles release a K block
+            mbar_init(&v_full[s], 1);
+            mbar_init(&v_empty[s], 1);
+        }
+        for (int i = 0; i < 4; ++i) {
+            mbar_init(&s_full[i], 1);
+            mbar_init(&p_full[i], 128);
+            mbar_init(&pv_done[i], 1);
+        }
+        *abort = 0;
+        fence_barrier_init();
+        prefetch_tensormap(&tm_q);
+        prefetch_tensormap(&tm_k);
+        prefetch_tensormap(&tm_v);
+    }
+    if (warp == 1) tmem_alloc(tmem_slot, TMEM_COLS);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp < 4) {
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 56;");
+        if (warp == 0 && lane == 0) {
+            // ---------------- TMA producer ----------------
+            ItemIter items(pa);
+            int bh, qb;
+            bool ok = true;
+            uint32_t ks = 0, kp = 0, vs = 0, vp = 0;  // ring positions
+            uint32_t n_q = 0;                         // items whose Q tiles have been requested
+            while (ok && items.next(bh, qb)) {
+                int64_t m0;
+                int nkv_t[2], nkv;
+                item_extent(a, qb, m0, nkv_t, nkv);
+#pragma unroll
+                for (int t = 0; t < 2; ++t) {
+                    ok = ok && mbar_wait(&q_empty[t], (n_q & 1) ^ 1, abort);  // the previous item's score products have read Q_t
+                    if (!ok) break;
+                    mbar_expect_tx(&q_full[t], L::QTILE);
+#pragma unroll
+                    for (int b = 0; b < D / 64; ++b)
+                        tma_load_3d(smem + L::Q_OFF + t * L::QTILE + b * (BM * 128), &tm_q, &q_full[t], b * 64, (int)(m0 + t * BM), bh);
+                }
+                if (!ok) break;
+                ++n_q;
+                for (int it = 0; it < 2 * nkv && ok; ++it) {  // K0, K1 V0, K2 V1, ..., V(n-1): the order of consumption
+                    const bool is_v = it == 2 * nkv - 1 || (it != 0 && (it & 1) == 0);
+                    const int j = it == 0 ? 0 : it == 2 * nkv - 1 ? nkv - 1 : is_v ? (it - 2) >> 1 : (it + 1) >> 1;
+                    uint32_t &st = is_v ? vs : ks, &ph = is_v ? vp : kp;
+                    uint64_t *full = is_v ? &v_full[st] : &k_full[st];
+                    ok = mbar_wait(is_v ? &v_empty[st] : &k_empty[st], ph ^ 1, abort);
+                    if (!ok) break;
+                    uint8_t *dst = smem + (is_v ? L::V_OFF : L::K_OFF) + st * L::TILE;
+                    mbar_expect_tx(full, L::TILE);
+                    const CUtensorMap *tm = is_v ? &tm_v : &tm_k;
+#pragma unroll
+                    for (int b = 0; b < D / 64; ++b) tma_load_3d(dst + b * (BNK * 128), tm, full, b * 64, j * BNK, bh);
+                    if (++st == STAGES) { st = 0; ph ^= 1; }
+                }
+            }
+            if (*abort) {  // drain our own copies before the CTA exits
+                if (n_q > 0)
+                    for (int t = 0; t < 2; ++t)
+                        for (uint32_t i = 0; i < (1u << 16) && !mbar_try_wait(&q_full[t], (n_q - 1) & 1); ++i) {}
+                for (uint32_t s = 0; s < (uint32_t)STAGES; ++s) {
+                    for (uint32_t i = 0; i < (1u << 16) && !mbar_try_wait(&k_full[s], s < ks ? kp : kp ^ 1); ++i) {}
+                    for (uint32_t i = 0; i < (1u << 16) && !mbar_try_wait(&v_full[s], s < vs ? vp : vp ^ 1); ++i) {}
+                }
+            }
+        } else if ((warp == 1 || warp == 2) && lane == 0) {
+            // ---------------- score issuers: warp 1 serves tile 0, warp 2 tile 1 ----------------
+            const int t = warp - 1;
+            const uint32_t idesc_s = idesc_f16(a.is_bf16, /*b_mn_major=*/false, BM, BNK);
+            constexpr uint32_t desc_hi = smem_desc_hi_sw128(1024);
+            const uint32_t q_lo = smem_desc_lo(smem_u32(smem + L::Q_OFF + t * L::QTILE), 16);
+            const uint32_t k_lo = smem_desc_lo(smem_u32(smem + L::K_OFF), 16);
+            const uint32_t s_tmem = tmem_base + t * 128;
+            uint32_t stage = 0, phase = 0;
+            uint32_t cs = 0;   // score blocks of this tile issued so far, over all items
+            uint32_t n_it = 0;
+            ItemIter items(pa);
+            int bh, qb;
+            bool ok = true;
+            while (ok && items.next(bh, qb)) {
+                int64_t m0;
+                int nkv_t[2], nkv;
+                item_extent(a, qb, m0, nkv_t, nkv);
+                const int my_nkv = nkv_t[t];
+                ok = mbar_wait(&q_full[t], n_it & 1, abort);
+                if (!ok) break;
+                if (t == 1 && n_it == 0) {  // tile 1 starts half a block period late: the two softmaxes take turns on the SFU
+                    const long long t_start = clock64();
+                    while (clock64() - t_start < kStaggerCycles) {}
+                }
+                ++n_it;
+                for (int j = 0; j < nkv && ok; ++j) {
+                    ok = mbar_wait(&k_full[stage], phase, abort);
+                    if (!ok) break;
+                    if (j < my_nkv) {
+                        const uint32_t b = cs & 1;
+                        // buffer b held S, then P, of this tile's block cs - 2: free once that P V has completed
+                        if (cs >= 2) ok = mbar_wait(&pv_done[t * 2 + b], ((cs - 2) >> 1) & 1, abort);
+                        if (!ok) break;
+                        tc_fence_after();
+                        const uint32_t kb = k_lo + stage * (L::TILE >> 4);
+                        const uint32_t d_tmem = s_tmem + b * BNK;
+#pragma unroll
+                        for (int kk = 0; kk < D / 16; ++kk)
+                            tc_mma_f16_halves(d_tmem, q_lo + (((kk >> 2) * (BM * 128) + (kk & 3) * 32) >> 4), desc_hi,
+                                              kb + (((kk >> 2) * (BNK * 128) + (kk & 3) * 32) >> 4), desc_hi, idesc_s, kk != 0);
+                        tc_commit(&s_full[t * 2 + b]);
+                        ++cs;
+                    }
+                    tc_commit(&k_empty[stage]);
+                    if (++stage == STAGES) { stage = 0; phase ^= 1; }
+                }
+                if (ok) tc_commit(&q_empty[t]);  // arrives when every score product of this item has read Q_t
+            }
+        } else if (warp == 3 && lane == 0) {
+            // ---------------- P V issuer, both tiles in turn ----------------
+            const uint32_t idesc_o = idesc_f16(a.is_bf16, /*b_mn_major=*/true, BM, D);
+            constexpr uint32_t desc_hi = smem_desc_hi_sw128(1024);
+            const uint32_t v_lo = smem_desc_lo(smem_u32(smem + L::V_OFF), BNK * 128);
+            uint32_t stage = 0, phase = 0;
+            uint32_t cp[2] = {0, 0};   // P blocks consumed per tile, over all items
+            uint32_t n_o[2] = {0, 0};  // items with work per tile
+            ItemIter items(pa);
+            int bh, qb;
+            bool ok = true;
+            while (ok && items.next(bh, qb)) {
+                int64_t m0;
+                int nkv_t[2], nkv;
+                item_extent(a, qb, m0, nkv_t, nkv);
+                for (int j = 0; j < nkv && ok; ++j) {
+                    ok = mbar_wait(&v_full[stage], phase, abort);
+                    if (!ok) break;
+                    const uint32_t vb = v_lo + stage * (L::TILE >> 4);
+#pragma unroll
+                    for (int t = 0; t < 2; ++t) {
+                        if (j >= nkv_t[t]) continue;
+                        const uint32_t b = cp[t] & 1;
+                        ok = mbar_wait(&p_full[t * 2 + b], (cp[t] >> 1) & 1, abort);
+                        // the first product of an item overwrites O_t: the previous item's epilogue must have read it
+                        if (ok && j == 0) ok = mbar_wait(&o_empty[t], (n_o[t] & 1) ^ 1, abort);
+                        if (!ok) break;
+                        tc_fence_after();
+                        const uint32_t p_tmem = tmem_base + t * 128 + b * BNK;
+#pragma unroll
+                        for (int kk = 0; kk < BNK / 16; ++kk)  // 16 keys = 8 packed columns of P, 16 rows = 2048 bytes of V
+                            tc_mma_f16_ts_halves(tmem_base + 256 + t * 128, p_tmem + kk * 8, vb + kk * (2048 >> 4), desc_hi, idesc_o, (j | kk) != 0);
+                        tc_commit(&pv_done[t * 2 + b]);
+                        ++cp[t];
+                        if (j == nkv_t[t] - 1) {
+                            tc_commit(&o_full[t]);
+                            ++n_o[t];
+                        }
+                    }
+                    if (!ok) break;
+                    tc_commit(&v_empty[stage]);
+                    if (++stage == STAGES) { stage = 0; phase ^= 1; }
+                }
+            }
+        }
+    } else {
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 224;");
+        // ---------------- softmax warpgroups: tile = warpgroup - 1 ----------------
+        const int t = (warp >> 2) - 1;
+        const int quarter = warp & 3;
+        const int r = quarter * 32 + lane;  // row inside the tile == TMEM lane
+        const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
+        const uint32_t t_s = tmem_base + lane_addr + t * 128;
+        const uint32_t t_o = tmem_base + lane_addr + 256 + t * 128;
+        uint32_t cs = 0, n_o = 0;
+        ItemIter items(pa);
+        int bh, qb;
+        bool ok = true;
+        while (ok && items.next(bh, qb)) {
+            int64_t m0;
+            int nkv_t[2], nkv;
+            item_extent(a, qb, m0, nkv_t, nkv);
+            const int my_nkv = nkv_t[t];
+            const int64_t tile_m0 = m0 + t * BM;
+            const int64_t row = tile_m0 + r;
+            float m_ref = -INFINITY, l = 0.0f;
+            for (int j = 0; j < my_nkv && ok; ++j) {
+                const uint32_t b = cs & 1;
+                ok = mbar_wait(&s_full[t * 2 + b], (cs >> 1) & 1, abort);
+                if (!ok) break;
+                tc_fence_after();
+                const int64_t n0 = (int64_t)j * BNK;
+                const bool need_mask = (n0 + BNK > a.seq) || (a.causal && n0 + BNK > tile_m0);
+                uint32_t sv[2][32];
+#pragma unroll
+                for (int c = 0; c < 2; ++c) tmem_ld_32x32(t_s + b * BNK + c * 32, sv[c]);
+                tmem_ld_wait();
+                float alpha;
+                bool rescale;
+                softmax_row<2, kPolyPairs>(sv, a.qk_scale, need_mask, n0, row, a.seq, a.causal, m_ref, l, alpha, rescale);
+                if (j > 0 && __any_sync(0xffffffffu, rescale)) {
+                    // O_t must be quiescent: P_t(j-1) V complete (P_t(j) V is not issued before this thread's arrival below)
+                    ok = mbar_wait(&pv_done[t * 2 + (b ^ 1)], ((cs - 1) >> 1) & 1, abort);
+                    if (!ok) break;
+                    tc_fence_after();
+#pragma unroll 1
+                    for (int c0 = 0; c0 < D; c0 += 32) {
+                        uint32_t v[32];
+                        tmem_ld_32x32(t_o + c0, v);
+                        tmem_ld_wait();
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * alpha);
+                        tmem_st_32x32(t_o + c0, v);
+                    }
+                }
+                uint32_t pk[32];
+#pragma unroll
+                for (int i = 0; i < 32; ++i) {
+                    const int e = 2 * i;
+                    pk[i] = pack_pair<T>(__uint_as_float(sv[e >> 5][e & 31]), __uint_as_float(sv[e >> 5][(e & 31) + 1]));
+                }
+                tmem_st_32x32(t_s + b * BNK, pk);
+                tmem_st_wait();
+                tc_fence_before();
+                mbar_arrive(&p_full[t * 2 + b]);
+                ++cs;
+            }
+            // ---- epilogue: O_t / l; the accumulator is handed back as soon as its last columns are in registers ----
+            if (ok && my_nkv > 0) {
+                ok = mbar_wait(&o_full[t], n_o & 1, abort);
+                if (!ok) break;
+                ++n_o;
+                tc_fence_after();
+                T *o = reinterpret_cast<T *>(a.o) + (int64_t)bh * a.stride_h + row * a.stride_m;
+#pragma unroll 1
+                for (int c0 = 0; c0 < D; c0 += 32) {
+                    uint32_t v[32];
+                    tmem_ld_32x32(t_o + c0, v);
+                    tmem_ld_wait();
+                    if (c0 + 32 == D) {
+                        tc_fence_before();
+                        mbar_arrive(&o_empty[t]);
+                    }
+                    if (row < a.seq) {
+                        float f[32];
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) f[i] = __fdiv_rn(__uint_as_float(v[i]), l);
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) *reinterpret_cast<uint4 *>(o + c0 + 8 * i) = Pack<T>::pack(f + 8 * i);
+                    }
+                }
+                if (a.lse && row < a.seq) a.lse[(int64_t)bh * a.seq + row] = (m_ref + log2f(l)) * LN2;
+            }
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (threadIdx.x == 0 && *abort) atomicExch(a.error, 4u);
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, TMEM_COLS);
+    }
+}
+
 // ---- CUDA-core kernel: any head_dim <= 128, any of the three dtypes, any strides -------------------
 // One CTA of 128 threads per (batch*head, 16 query rows): 8 threads share a row and split head_dim.
 template <typename T>
@@ -1027,7 +1393,9 @@ __global__ void __launch_bounds__(128) attention_simple_kernel(const T *q, const
     }
 }
 
-constexpr int ATTN_VARIANTS = 4;  // 0: two 128-row query tiles per CTA, P in TMEM; 1, 2: one tile, P through shared memory, 4- or 3-deep K/V ring
+// 0: two 128-row query tiles per CTA, 128-key blocks, P in TMEM; 1, 2: one tile, P through shared memory, 4- or 3-deep
+// K/V ring; 3: two tiles, 64-key blocks, one CTA per 256 query rows; 4: the same as persistent CTAs over a static schedule
+constexpr int ATTN_VARIANTS = 5;
 
 // Tensor maps over [bh, seq, D] with boxes of 64 values x 128 rows (64 rows for K and V when KV_ROWS is 64),
 // then the launch.  TILES = query tiles of 128 rows per CTA.
@@ -1052,6 +1420,73 @@ int launch_tc(const void *q, const void *k, const void *v, const AttnArgs &args,
     return check_launch("enc_attention_fwd");
 }
 
+// Query-block order inside a slice for the persistent kernel's zigzag schedule (see attention_p64_kernel): the two
+// items a CTA gets in rounds 2m and 2m+1 are k1 = 2mG + c and k2 = (2m+1)G + G-1-c, so their positions inside a slice
+// satisfy q1 + q2 = (4m+2)G - 1 (mod n), which is the same s for every m when 4G is a multiple of n.  Positions that
+// pair up get query blocks that add up to n-1, i.e. causal key-block counts that add up to a constant.
+void balance_perm(int G, int n, uint8_t *perm) {
+    for (int q = 0; q < n; ++q) perm[q] = (uint8_t)q;
+    if (n > 64 || n < 2) return;
+    const int s = (int)(((2LL * G - 1) % n + n) % n);
+    int assigned[64];
+    bool used[64] = {};
+    for (int q = 0; q < n; ++q) assigned[q] = -1;
+    int lo = 0;
+    for (int q = 0; q < n; ++q) {
+        const int q2 = ((s - q) % n + n) % n;
+        if (assigned[q] >= 0 || q2 == q) continue;
+        assigned[q] = lo;
+        assigned[q2] = n - 1 - lo;
+        used[lo] = used[n - 1 - lo] = true;
+        ++lo;
+    }
+    int next = 0;
+    for (int q = 0; q < n; ++q) {  // positions paired with themselves take the values that are left (the middle ones)
+        if (assigned[q] >= 0) continue;
+        while (used[next]) ++next;
+        assigned[q] = next;
+        used[next] = true;
+    }
+    for (int q = 0; q < n; ++q) perm[q] = (uint8_t)assigned[q];
+}
+
+template <typename T, int D, int STAGES>
+int launch_persistent(const void *q, const void *k, const void *v, const AttnArgs &args, int64_t bh, cudaStream_t st) {
+    char err[256];
+    CUtensorMap tq, tk, tv;
+    const uint64_t dims[3] = {(uint64_t)D, (uint64_t)args.seq, (uint64_t)bh};
+    const uint64_t strides[2] = {(uint64_t)args.stride_m * 2, (uint64_t)args.stride_h * 2};
+    const uint32_t box[3] = {64, BM, 1}, kv_box[3] = {64, BN64, 1};
+    if (!make_tensor_map(&tq, q, args.is_bf16, 3, dims, strides, box, err, sizeof(err)) ||
+        !make_tensor_map(&tk, k, args.is_bf16, 3, dims, strides, kv_box, err, sizeof(err)) ||
+        !make_tensor_map(&tv, v, args.is_bf16, 3, dims, strides, kv_box, err, sizeof(err)))
+        return fail(ENC_ERR_LAUNCH, "enc_attention_fwd: %s", err);
+    auto kern = attention_p64_kernel<T, D, STAGES>;
+    const int smem = AttnSmemP<D, STAGES>::TOTAL + 1024;
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) return fail(ENC_ERR_LAUNCH, "enc_attention_fwd: cannot opt in to %d bytes of shared memory: %s", smem, cudaGetErrorString(e));
+    PersistArgs pa;
+    pa.a = args;
+    pa.n_qb = (int)cdiv(args.seq, 2 * BM);
+    const int64_t items = (int64_t)pa.n_qb * bh;
+    if (items > 0x7fffffffLL) return fail(ENC_ERR_UNSUPPORTED, "enc_attention_fwd: more than 2^31-1 work items");
+    pa.n_items = (int)items;
+    int grid = device_props().sm_count;
+    for (int i = 0; i < 64; ++i) pa.perm[i] = (uint8_t)i;
+    if (args.causal && pa.n_qb >= 2 && pa.n_qb <= 64 && items > grid) {
+        // the pairing needs 4 * grid to be a multiple of n_qb: give up a few SMs (at most 5%) for it when necessary
+        int g = grid;
+        while (g > 0 && (4LL * g) % pa.n_qb != 0) --g;
+        if (g * 20 >= grid * 19) {
+            grid = g;
+            balance_perm(grid, pa.n_qb, pa.perm);
+        }
+    }
+    if (grid > items) grid = (int)items;
+    kern<<<(unsigned)grid, kThreads2, smem, st>>>(tq, tk, tv, pa);
+    return check_launch("enc_attention_fwd");
+}
+
 template <typename T>
 int launch_attention(const void *q, const void *k, const void *v, AttnArgs args, int64_t bh, int64_t d, int variant,
                      cudaStream_t st) {
@@ -1069,7 +1504,8 @@ int launch_attention(const void *q, const void *k, const void *v, AttnArgs args,
     args.error = device_error_word();
     if (!args.error) return fail(ENC_ERR_NO_MEMORY, "enc_attention_fwd: cannot allocate the device status word");
     if constexpr (sizeof(T) == 2) {
-        if (variant < 0) variant = args.seq > BM ? 3 : 1;  // two tiles per CTA once there are two tiles
+        if (variant < 0) variant = args.seq > BM ? 4 : 1;  // two tiles per CTA once there are two tiles
+        if (variant == 4) return d == 128 ? launch_persistent<T, 128, 5>(q, k, v, args, bh, st) : launch_persistent<T, 64, 6>(q, k, v, args, bh, st);
         if (d == 128) {
             if (variant == 0) return launch_tc<T, 128, 5, 2>(q, k, v, args, bh, st);
             if (variant == 3) return launch_tc<T, 128, 5, 2, 64>(q, k, v, args, bh, st);
@@ -1088,6 +1524,7 @@ int attention_variants() { return ATTN_VARIANTS; }
 void attention_variant_info(int v, char *out, size_t n) {
     if (v == 0) snprintf(out, n, "block_m=256 (two 128-row tiles, one softmax warpgroup each) block_n=128 tcgen05 S/P/O in TMEM");
     else if (v == 3) snprintf(out, n, "block_m=256 (two 128-row tiles) block_n=64 tcgen05 S/P/O in TMEM, score products issued one block ahead");
+    else if (v == 4) snprintf(out, n, "block_m=256 block_n=64 as variant 3, persistent CTAs (one per SM) over a static balanced schedule");
     else snprintf(out, n, "block_m=128 block_n=128 kv_stages=%d tcgen05 S/O in TMEM, P through shared memory", v == 2 ? 3 : 4);
 }
 
