@@ -145,6 +145,36 @@ __device__ __forceinline__ void softmax_row(uint32_t (&sv)[NCH][32], float qk_sc
     row_exp<NCH, POLY_PAIRS>(sv, qk_scale, mx_raw, m_ref, l, alpha, rescale);
 }
 
+// The same with the mask given as a limit: element e of the block (key col0 + e) is masked when e > lim, where
+// lim = min(row, seq - 1) - col0 under a causal mask and seq - 1 - col0 otherwise.  One 32-bit compare per element
+// against a value that is fixed per row and block; the kernels for sequences below 2^31 use this form.
+template <int NCH>
+__device__ __forceinline__ float row_mask_max_lim(uint32_t (&sv)[NCH][32], bool need_mask, int lim) {
+    if (need_mask) {
+#pragma unroll
+        for (int c = 0; c < NCH; ++c)
+#pragma unroll
+            for (int i = 0; i < 32; ++i)
+                if (c * 32 + i > lim) sv[c][i] = __float_as_uint(-INFINITY);
+    }
+    float mx0 = -INFINITY, mx1 = -INFINITY;
+#pragma unroll
+    for (int c = 0; c < NCH; ++c)
+#pragma unroll
+        for (int i = 0; i < 32; i += 4) {
+            mx0 = max3(mx0, __uint_as_float(sv[c][i]), __uint_as_float(sv[c][i + 1]));
+            mx1 = max3(mx1, __uint_as_float(sv[c][i + 2]), __uint_as_float(sv[c][i + 3]));
+        }
+    return fmaxf(mx0, mx1);
+}
+
+template <int NCH, int POLY_PAIRS = 0>
+__device__ __forceinline__ void softmax_row_lim(uint32_t (&sv)[NCH][32], float qk_scale, bool need_mask, int lim, float &m_ref, float &l,
+                                                float &alpha, bool &rescale) {
+    const float mx_raw = row_mask_max_lim<NCH>(sv, need_mask, lim);
+    row_exp<NCH, POLY_PAIRS>(sv, qk_scale, mx_raw, m_ref, l, alpha, rescale);
+}
+
 // P row into shared memory in the swizzled K-major layout the MMA reads: 64-wide boxes, 128-byte rows,
 // 16-byte chunk index XOR (row & 7).
 template <typename T> __device__ __forceinline__ void store_p_row(uint8_t *p_row, int r, const uint32_t (&sv)[4][32]) {
@@ -886,7 +916,8 @@ attention_ts64_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
             tmem_ld_wait();
             float alpha;
             bool rescale;
-            softmax_row<2, kPolyPairs>(sv, a.qk_scale, need_mask, n0, row, a.seq, a.causal, m_ref, l, alpha, rescale);
+            const int64_t last = a.causal && row < a.seq ? row : a.seq - 1;  // last key this row sees
+            softmax_row_lim<2, kPolyPairs>(sv, a.qk_scale, need_mask, (int)(last - n0), m_ref, l, alpha, rescale);
             if (j > 0 && __any_sync(0xffffffffu, rescale)) {
                 // O_t must be quiescent: P_t(j-1) V complete (P_t(j) V is not issued before this thread's arrival below)
                 ok = mbar_wait(&pv_done[t * 2 + (b ^ 1)], ((j - 1) >> 1) & 1, abort);
@@ -962,33 +993,32 @@ attention_ts64_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
 // k = r G + (G-1-c) in odd ones.  Consecutive items share a slice, so the CTAs of a round read a few slices' K / V
 // from L2 as the one-shot grid does.  For causal launches `perm` pairs the query blocks so that the two items a
 // CTA gets in an even/odd pair of rounds have a constant total number of key blocks (the host builds it from
-// (G, n_qb); see balance_perm): 98.8% balance for 4096 items on 148 SMs, with no work counter in global memory.
-struct PersistArgs {
-    AttnArgs a;
-    int n_qb;      // query blocks of 256 rows per slice
-    int n_items;   // n_qb * slices
-    uint8_t perm[64];  // query-block order inside a slice (identity beyond 64 blocks)
+// (G, n_qb); see balance_perm16): 98.8% balance for 4096 items on 148 SMs, with no work counter in global memory.
+// (The schedule travels as plain scalar kernel parameters, which the hardware reads as constant-bank operands.  A
+// struct parameter whose address is taken - a reference to it, a pointer to a table inside it - is read through
+// generic loads instead, a few hundred cycles each, and the loops below re-read their parameters after every
+// barrier wait: that alone cost 18% when first measured.)
+struct Sched {
+    int n_qb;         // query blocks of 256 rows per slice
+    int n_items;      // n_qb * slices
+    uint64_t perm16;  // query-block order inside a slice, 4 bits per position (identity when n_qb > 16)
 };
 
-struct ItemIter {
-    int G, c, n_items, n_qb, r;
-    const uint8_t *perm;
-    __device__ ItemIter(const PersistArgs &p) : G((int)gridDim.x), c((int)blockIdx.x), n_items(p.n_items), n_qb(p.n_qb), r(0), perm(p.perm) {}
-    // next item of this CTA: false when there is none left
-    __device__ bool next(int &bh, int &qb) {
-        for (;; ++r) {
-            const long long base = (long long)r * G;
-            if (base >= n_items) return false;
-            const long long k = base + ((r & 1) ? G - 1 - c : c);
-            if (k >= n_items) continue;
-            bh = (int)(k / n_qb);
-            const int q = (int)(k % n_qb);
-            qb = n_qb <= 64 ? perm[q] : q;
-            ++r;
-            return true;
-        }
-    }
-};
+// Work item of this CTA in round r: false when the round has none for it.  The round loop of every role has a
+// trip count that depends on kernel parameters and the grid only, and a failed wait skips the remaining rounds
+// with `continue` instead of leaving the loop: that keeps r, and everything derived from it (slice, query block,
+// row offsets, key-block counts), uniform in the compiler's eyes, so that it lives in uniform registers as the
+// blockIdx-derived values of the one-shot kernel do.  (With a `while (ok && next())` loop none of it was, and the
+// softmax loop lost 12% to the extra vector registers and instructions.)
+__device__ __forceinline__ bool item_of_round(int r, int n_items, int n_qb, uint64_t perm16, int &bh, int &qb) {
+    const int G = (int)gridDim.x, c = (int)blockIdx.x;
+    const int k = r * G + ((r & 1) ? G - 1 - c : c);
+    if (k >= n_items) return false;
+    bh = k / n_qb;
+    const int q = k - bh * n_qb;
+    qb = n_qb <= 16 ? (int)((perm16 >> (4 * q)) & 15) : q;
+    return true;
+}
 
 // key blocks of 64 the two tiles of query block qb need
 __device__ __forceinline__ void item_extent(const AttnArgs &a, int qb, int64_t &m0, int (&nkv_t)[2], int &nkv) {
@@ -1016,10 +1046,9 @@ template <int D, int STAGES> struct AttnSmemP {  // like AttnSmem64, with per-ti
 template <typename T, int D, int STAGES>
 __global__ void __launch_bounds__(kThreads2, 1)
 attention_p64_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
-                     const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ PersistArgs pa) {
+                     const __grid_constant__ CUtensorMap tm_v, AttnArgs a, Sched sc) {
     using L = AttnSmemP<D, STAGES>;
     constexpr int BNK = BN64;
-    const AttnArgs &a = pa.a;
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint64_t *q_full = reinterpret_cast<uint64_t *>(smem + L::BAR_OFF);  // [2]
@@ -1038,6 +1067,7 @@ attention_p64_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     constexpr uint32_t TMEM_COLS = 512;
+    const int rounds = (sc.n_items + (int)gridDim.x - 1) / (int)gridDim.x;
 
     if (threadIdx.x == 0) {
         for (int t = 0; t < 2; ++t) {
@@ -1070,15 +1100,20 @@ attention_p64_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
     const uint32_t tmem_base = *tmem_slot;
 
     if (warp < 4) {
-        asm volatile("setmaxnreg.dec.sync.aligned.u32 56;");
+        // Register budget: the CTA's pool is what it was launched with, 384 threads x 168 registers.  setmaxnreg.inc blocks
+        // until the pool has the registers, for ever if it never can: 128 x dec + 256 x inc must not exceed 384 x 168,
+        // i.e. dec + 2 inc <= 504.  The persistent producer / issuer loops do not fit in 56 registers (they spilled,
+        // and a spill reload in front of every MMA showed up as 7% less tensor-pipe activity): 72 + 2 x 216 = 504.
+        static_assert(72 + 2 * 216 <= 3 * 168, "setmaxnreg budget");
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 72;");
         if (warp == 0 && lane == 0) {
             // ---------------- TMA producer ----------------
-            ItemIter items(pa);
-            int bh, qb;
             bool ok = true;
             uint32_t ks = 0, kp = 0, vs = 0, vp = 0;  // ring positions
             uint32_t n_q = 0;                         // items whose Q tiles have been requested
-            while (ok && items.next(bh, qb)) {
+            for (int r = 0; r < rounds; ++r) {
+                int bh, qb;
+                if (!item_of_round(r, sc.n_items, sc.n_qb, sc.perm16, bh, qb) || !ok) continue;
                 int64_t m0;
                 int nkv_t[2], nkv;
                 item_extent(a, qb, m0, nkv_t, nkv);
@@ -1091,7 +1126,7 @@ attention_p64_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
                     for (int b = 0; b < D / 64; ++b)
                         tma_load_3d(smem + L::Q_OFF + t * L::QTILE + b * (BM * 128), &tm_q, &q_full[t], b * 64, (int)(m0 + t * BM), bh);
                 }
-                if (!ok) break;
+                if (!ok) continue;
                 ++n_q;
                 for (int it = 0; it < 2 * nkv && ok; ++it) {  // K0, K1 V0, K2 V1, ..., V(n-1): the order of consumption
                     const bool is_v = it == 2 * nkv - 1 || (it != 0 && (it & 1) == 0);
@@ -1128,16 +1163,16 @@ attention_p64_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
             uint32_t stage = 0, phase = 0;
             uint32_t cs = 0;   // score blocks of this tile issued so far, over all items
             uint32_t n_it = 0;
-            ItemIter items(pa);
-            int bh, qb;
             bool ok = true;
-            while (ok && items.next(bh, qb)) {
+            for (int r = 0; r < rounds; ++r) {
+                int bh, qb;
+                if (!item_of_round(r, sc.n_items, sc.n_qb, sc.perm16, bh, qb) || !ok) continue;
                 int64_t m0;
                 int nkv_t[2], nkv;
                 item_extent(a, qb, m0, nkv_t, nkv);
-                const int my_nkv = nkv_t[t];
+                const int my_nkv = t == 0 ? nkv_t[0] : nkv_t[1];
                 ok = mbar_wait(&q_full[t], n_it & 1, abort);
-                if (!ok) break;
+                if (!ok) continue;
                 if (t == 1 && n_it == 0) {  // tile 1 starts half a block period late: the two softmaxes take turns on the SFU
                     const long long t_start = clock64();
                     while (clock64() - t_start < kStaggerCycles) {}
@@ -1172,39 +1207,42 @@ attention_p64_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
             constexpr uint32_t desc_hi = smem_desc_hi_sw128(1024);
             const uint32_t v_lo = smem_desc_lo(smem_u32(smem + L::V_OFF), BNK * 128);
             uint32_t stage = 0, phase = 0;
-            uint32_t cp[2] = {0, 0};   // P blocks consumed per tile, over all items
-            uint32_t n_o[2] = {0, 0};  // items with work per tile
-            ItemIter items(pa);
-            int bh, qb;
+            // per-tile counters as scalars (an array indexed by the tile lands in local memory, and a reload in front of
+            // every product is a few hundred cycles on the thread that feeds the tensor core)
+            uint32_t cp0 = 0, cp1 = 0;    // P blocks consumed per tile, over all items
+            uint32_t n_o0 = 0, n_o1 = 0;  // items with work per tile
             bool ok = true;
-            while (ok && items.next(bh, qb)) {
+            for (int r = 0; r < rounds; ++r) {
+                int bh, qb;
+                if (!item_of_round(r, sc.n_items, sc.n_qb, sc.perm16, bh, qb) || !ok) continue;
                 int64_t m0;
                 int nkv_t[2], nkv;
                 item_extent(a, qb, m0, nkv_t, nkv);
+                const int nkv0 = nkv_t[0], nkv1 = nkv_t[1];
                 for (int j = 0; j < nkv && ok; ++j) {
                     ok = mbar_wait(&v_full[stage], phase, abort);
                     if (!ok) break;
                     const uint32_t vb = v_lo + stage * (L::TILE >> 4);
-#pragma unroll
-                    for (int t = 0; t < 2; ++t) {
-                        if (j >= nkv_t[t]) continue;
-                        const uint32_t b = cp[t] & 1;
-                        ok = mbar_wait(&p_full[t * 2 + b], (cp[t] >> 1) & 1, abort);
+                    auto product = [&](const int t, const int my_nkv, uint32_t &cp, uint32_t &n_o) -> bool {
+                        if (j >= my_nkv) return true;
+                        const uint32_t b = cp & 1;
+                        if (!mbar_wait(&p_full[t * 2 + b], (cp >> 1) & 1, abort)) return false;
                         // the first product of an item overwrites O_t: the previous item's epilogue must have read it
-                        if (ok && j == 0) ok = mbar_wait(&o_empty[t], (n_o[t] & 1) ^ 1, abort);
-                        if (!ok) break;
+                        if (j == 0 && !mbar_wait(&o_empty[t], (n_o & 1) ^ 1, abort)) return false;
                         tc_fence_after();
                         const uint32_t p_tmem = tmem_base + t * 128 + b * BNK;
 #pragma unroll
                         for (int kk = 0; kk < BNK / 16; ++kk)  // 16 keys = 8 packed columns of P, 16 rows = 2048 bytes of V
                             tc_mma_f16_ts_halves(tmem_base + 256 + t * 128, p_tmem + kk * 8, vb + kk * (2048 >> 4), desc_hi, idesc_o, (j | kk) != 0);
                         tc_commit(&pv_done[t * 2 + b]);
-                        ++cp[t];
-                        if (j == nkv_t[t] - 1) {
+                        ++cp;
+                        if (j == my_nkv - 1) {
                             tc_commit(&o_full[t]);
-                            ++n_o[t];
+                            ++n_o;
                         }
-                    }
+                        return true;
+                    };
+                    ok = product(0, nkv0, cp0, n_o0) && product(1, nkv1, cp1, n_o1);
                     if (!ok) break;
                     tc_commit(&v_empty[stage]);
                     if (++stage == STAGES) { stage = 0; phase ^= 1; }
@@ -1212,7 +1250,7 @@ attention_p64_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
             }
         }
     } else {
-        asm volatile("setmaxnreg.inc.sync.aligned.u32 224;");
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 216;");
         // ---------------- softmax warpgroups: tile = warpgroup - 1 ----------------
         const int t = (warp >> 2) - 1;
         const int quarter = warp & 3;
@@ -1221,31 +1259,33 @@ attention_p64_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
         const uint32_t t_s = tmem_base + lane_addr + t * 128;
         const uint32_t t_o = tmem_base + lane_addr + 256 + t * 128;
         uint32_t cs = 0, n_o = 0;
-        ItemIter items(pa);
-        int bh, qb;
         bool ok = true;
-        while (ok && items.next(bh, qb)) {
+        for (int r0 = 0; r0 < rounds; ++r0) {
+            int bh, qb;
+            if (!item_of_round(r0, sc.n_items, sc.n_qb, sc.perm16, bh, qb) || !ok) continue;
             int64_t m0;
             int nkv_t[2], nkv;
             item_extent(a, qb, m0, nkv_t, nkv);
-            const int my_nkv = nkv_t[t];
-            const int64_t tile_m0 = m0 + t * BM;
-            const int64_t row = tile_m0 + r;
+            const int my_nkv = t == 0 ? nkv_t[0] : nkv_t[1];
+            const int seq = (int)a.seq;  // below 2^31 on this path
+            const int tile_m0 = (int)m0 + t * BM;
+            const int row = tile_m0 + r;
+            const int last = a.causal && row < seq ? row : seq - 1;  // last key this row sees
             float m_ref = -INFINITY, l = 0.0f;
             for (int j = 0; j < my_nkv && ok; ++j) {
                 const uint32_t b = cs & 1;
                 ok = mbar_wait(&s_full[t * 2 + b], (cs >> 1) & 1, abort);
                 if (!ok) break;
                 tc_fence_after();
-                const int64_t n0 = (int64_t)j * BNK;
-                const bool need_mask = (n0 + BNK > a.seq) || (a.causal && n0 + BNK > tile_m0);
+                const int n0 = j * BNK;
+                const bool need_mask = (n0 + BNK > seq) || (a.causal && n0 + BNK > tile_m0);
                 uint32_t sv[2][32];
 #pragma unroll
                 for (int c = 0; c < 2; ++c) tmem_ld_32x32(t_s + b * BNK + c * 32, sv[c]);
                 tmem_ld_wait();
                 float alpha;
                 bool rescale;
-                softmax_row<2, kPolyPairs>(sv, a.qk_scale, need_mask, n0, row, a.seq, a.causal, m_ref, l, alpha, rescale);
+                softmax_row_lim<2, kPolyPairs>(sv, a.qk_scale, need_mask, last - n0, m_ref, l, alpha, rescale);
                 if (j > 0 && __any_sync(0xffffffffu, rescale)) {
                     // O_t must be quiescent: P_t(j-1) V complete (P_t(j) V is not issued before this thread's arrival below)
                     ok = mbar_wait(&pv_done[t * 2 + (b ^ 1)], ((cs - 1) >> 1) & 1, abort);
@@ -1276,10 +1316,10 @@ attention_p64_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
             // ---- epilogue: O_t / l; the accumulator is handed back as soon as its last columns are in registers ----
             if (ok && my_nkv > 0) {
                 ok = mbar_wait(&o_full[t], n_o & 1, abort);
-                if (!ok) break;
+                if (!ok) continue;
                 ++n_o;
                 tc_fence_after();
-                T *o = reinterpret_cast<T *>(a.o) + (int64_t)bh * a.stride_h + row * a.stride_m;
+                T *o = reinterpret_cast<T *>(a.o) + (int64_t)bh * a.stride_h + (int64_t)row * a.stride_m;
 #pragma unroll 1
                 for (int c0 = 0; c0 < D; c0 += 32) {
                     uint32_t v[32];
@@ -1289,7 +1329,7 @@ attention_p64_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
                         tc_fence_before();
                         mbar_arrive(&o_empty[t]);
                     }
-                    if (row < a.seq) {
+                    if (row < seq) {
                         float f[32];
 #pragma unroll
                         for (int i = 0; i < 32; ++i) f[i] = __fdiv_rn(__uint_as_float(v[i]), l);
@@ -1297,7 +1337,7 @@ attention_p64_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
                         for (int i = 0; i < 4; ++i) *reinterpret_cast<uint4 *>(o + c0 + 8 * i) = Pack<T>::pack(f + 8 * i);
                     }
                 }
-                if (a.lse && row < a.seq) a.lse[(int64_t)bh * a.seq + row] = (m_ref + log2f(l)) * LN2;
+                if (a.lse && row < seq) a.lse[(int64_t)bh * a.seq + row] = (m_ref + log2f(l)) * LN2;
             }
         }
     }
@@ -1424,12 +1464,13 @@ int launch_tc(const void *q, const void *k, const void *v, const AttnArgs &args,
 // items a CTA gets in rounds 2m and 2m+1 are k1 = 2mG + c and k2 = (2m+1)G + G-1-c, so their positions inside a slice
 // satisfy q1 + q2 = (4m+2)G - 1 (mod n), which is the same s for every m when 4G is a multiple of n.  Positions that
 // pair up get query blocks that add up to n-1, i.e. causal key-block counts that add up to a constant.
-void balance_perm(int G, int n, uint8_t *perm) {
-    for (int q = 0; q < n; ++q) perm[q] = (uint8_t)q;
-    if (n > 64 || n < 2) return;
+uint64_t balance_perm16(int G, int n) {
+    uint64_t identity = 0;
+    for (int q = 0; q < 16; ++q) identity |= (uint64_t)q << (4 * q);
+    if (n > 16 || n < 2) return identity;
     const int s = (int)(((2LL * G - 1) % n + n) % n);
-    int assigned[64];
-    bool used[64] = {};
+    int assigned[16];
+    bool used[16] = {};
     for (int q = 0; q < n; ++q) assigned[q] = -1;
     int lo = 0;
     for (int q = 0; q < n; ++q) {
@@ -1447,7 +1488,9 @@ void balance_perm(int G, int n, uint8_t *perm) {
         assigned[q] = next;
         used[next] = true;
     }
-    for (int q = 0; q < n; ++q) perm[q] = (uint8_t)assigned[q];
+    uint64_t perm = 0;
+    for (int q = 0; q < n; ++q) perm |= (uint64_t)assigned[q] << (4 * q);
+    return perm;
 }
 
 template <typename T, int D, int STAGES>
@@ -1465,25 +1508,24 @@ int launch_persistent(const void *q, const void *k, const void *v, const AttnArg
     const int smem = AttnSmemP<D, STAGES>::TOTAL + 1024;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return fail(ENC_ERR_LAUNCH, "enc_attention_fwd: cannot opt in to %d bytes of shared memory: %s", smem, cudaGetErrorString(e));
-    PersistArgs pa;
-    pa.a = args;
-    pa.n_qb = (int)cdiv(args.seq, 2 * BM);
-    const int64_t items = (int64_t)pa.n_qb * bh;
+    Sched sc;
+    sc.n_qb = (int)cdiv(args.seq, 2 * BM);
+    const int64_t items = (int64_t)sc.n_qb * bh;
     if (items > 0x7fffffffLL) return fail(ENC_ERR_UNSUPPORTED, "enc_attention_fwd: more than 2^31-1 work items");
-    pa.n_items = (int)items;
+    sc.n_items = (int)items;
     int grid = device_props().sm_count;
-    for (int i = 0; i < 64; ++i) pa.perm[i] = (uint8_t)i;
-    if (args.causal && pa.n_qb >= 2 && pa.n_qb <= 64 && items > grid) {
+    sc.perm16 = balance_perm16(grid, 0);  // identity
+    if (args.causal && sc.n_qb >= 2 && sc.n_qb <= 16 && items > grid) {
         // the pairing needs 4 * grid to be a multiple of n_qb: give up a few SMs (at most 5%) for it when necessary
         int g = grid;
-        while (g > 0 && (4LL * g) % pa.n_qb != 0) --g;
+        while (g > 0 && (4LL * g) % sc.n_qb != 0) --g;
         if (g * 20 >= grid * 19) {
             grid = g;
-            balance_perm(grid, pa.n_qb, pa.perm);
+            sc.perm16 = balance_perm16(grid, sc.n_qb);
         }
     }
     if (grid > items) grid = (int)items;
-    kern<<<(unsigned)grid, kThreads2, smem, st>>>(tq, tk, tv, pa);
+    kern<<<(unsigned)grid, kThreads2, smem, st>>>(tq, tk, tv, args, sc);
     return check_launch("enc_attention_fwd");
 }
 
@@ -1504,7 +1546,16 @@ int launch_attention(const void *q, const void *k, const void *v, AttnArgs args,
     args.error = device_error_word();
     if (!args.error) return fail(ENC_ERR_NO_MEMORY, "enc_attention_fwd: cannot allocate the device status word");
     if constexpr (sizeof(T) == 2) {
-        if (variant < 0) variant = args.seq > BM ? 4 : 1;  // two tiles per CTA once there are two tiles
+        if (variant < 0) {
+            // Two tiles per CTA once there are two tiles.  Measured on B200 (bf16/f16, D = 128 and 64): the one-shot grid
+            // (variant 3) is 5-12% faster than the persistent kernel wherever the hardware's own dynamic dispatch of CTAs
+            // balances well - many CTAs per SM, or at most one - because the persistent kernel's inner loops run slower (its
+            // code keeps more per-item state live next to the softmax registers), which its saved set-up time (about 5% of a
+            // 256-row item at 4096 keys) does not pay back.  The persistent kernel wins (by 20-26%) where dispatch order
+            // cannot balance: causal launches with between one and two items per SM, e.g. [1, 16, 4096, D].
+            const int64_t items = cdiv(args.seq, 2 * BM) * bh, sms = device_props().sm_count;
+            variant = args.seq <= BM ? 1 : (args.causal && items > sms && items <= 2 * sms && args.seq >= 12 * 2 * BM) ? 4 : 3;
+        }
         if (variant == 4) return d == 128 ? launch_persistent<T, 128, 5>(q, k, v, args, bh, st) : launch_persistent<T, 64, 6>(q, k, v, args, bh, st);
         if (d == 128) {
             if (variant == 0) return launch_tc<T, 128, 5, 2>(q, k, v, args, bh, st);

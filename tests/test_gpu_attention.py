@@ -80,6 +80,30 @@ def test_attention_every_variant_and_fallback(oracle):
                       torch_of(np.zeros((1, 1, 8, 48), np.float16)))
 
 
+@pytest.mark.parametrize("causal", [False, True])
+@pytest.mark.parametrize("shape,dt", [((4, 64, 512, 128), BF16), ((2, 50, 640, 128), F16), ((3, 70, 1000, 64), BF16),
+                                      ((1, 160, 300, 128), F16)], ids=str)
+def test_attention_many_items_per_cta(oracle, causal, shape, dt):
+    """More work items (256 query rows of one (batch, head) slice) than SMs, so that every persistent CTA walks
+    several items back to back: rings and barrier phases carry over from one item to the next, the last query
+    block is ragged (640 rows: its second tile is empty; 1000 and 300 rows: partly filled), and with a causal
+    mask the two tiles of an item need different numbers of key blocks.  Every variant must agree."""
+    z, h, s_, d = shape
+    r = np.random.default_rng(s_ + d + h)
+    q, k, v = (r.standard_normal(shape).astype(np.float32).astype(dt) for _ in range(3))
+    want, want_lse = oracle.attention(q, k, v, causal, None, 128, 128, return_lse=True)
+    qt, kt, vt = torch_of(q), torch_of(k), torch_of(v)
+    o, lse = ops.attention(qt, kt, vt, causal, return_lse=True)
+    assert_close(host(o), want, atol=ATOL[dt])
+    np.testing.assert_allclose(host(lse), want_lse, atol=1e-3, rtol=0)
+    for variant in (3, 4):
+        o2 = enceladus.new_empty(qt)
+        ops.attention_kernel[(enceladus.cdiv(s_, 128), z * h)](qt, kt, vt, o2, d**-0.5, s_, s_ * d, d, HEAD_DIM=d, BLOCK_M=128,
+                                                               BLOCK_N=128, CAUSAL=causal, variant=variant)
+        assert_close(host(o2), want, atol=ATOL[dt], what=f"variant {variant}")
+    enceladus.synchronize()  # raises if a bounded wait ran out
+
+
 def test_attention_config4_slices_and_properties(oracle):
     """Full benchmark shape [8, 32, 4096, 128] bf16: two (batch, head) slices against the oracle, all of it
     against properties that hold for any size."""
