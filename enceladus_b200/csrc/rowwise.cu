@@ -119,9 +119,10 @@ __device__ __forceinline__ void process_row(const RowRegs<T, V> &x, const RowArg
     };
 
     constexpr float LOG2E = 1.4426950408889634f;
-    // Softmax needs every exponential twice (row sum, output).  For float32 rows they are kept in registers; for
-    // 16-bit rows, which sit packed in half as many registers, they are recomputed.
-    constexpr bool KEEP_EXP = OP == OP_SOFTMAX && sizeof(T) == 4;
+    // Softmax needs every exponential twice (row sum, output).  They are kept in registers (as float32) when a thread
+    // holds at most 64 elements of the row: always for float32 rows, and for 16-bit rows once the row is spread over
+    // twice the minimum number of threads (the launcher's default for wide 16-bit rows); otherwise they are recomputed.
+    constexpr bool KEEP_EXP = OP == OP_SOFTMAX && V * NV <= 64;
     float ex[KEEP_EXP ? V * NV : 1];
     float s0 = 1.0f, s1 = 0.0f;  // softmax: -max*log2e, 1/sum.  layernorm: rstd, -mean*rstd.  rmsnorm: rstd.
     if (OP == OP_SOFTMAX) {
@@ -309,6 +310,9 @@ __global__ void __launch_bounds__(512) row_kernel(RowArgs a) {
     const int64_t row = (int64_t)blockIdx.x * rows_per_cta + threadIdx.x / tpr;
     const bool live = row < a.rows;
     const T *xr = reinterpret_cast<const T *>(a.x) + (live ? row : 0) * a.stride_x;
+    // (Asking L2 for the whole input with bulk prefetches before the dependency wait, from the first CTA of every SM, was
+    // measured on the small shapes it could help and lost 5-10%: the CTAs that issue the prefetches start their own
+    // rows late.)
     grid_dependency_wait();  // launched with launch_overlapped(): nothing above touches global memory
 
     RowRegs<T, V> x;
@@ -565,9 +569,15 @@ int launch_rows(RowArgs a, int variant, cudaStream_t st, const char *name) {
     if (a.rows > 0x7fffffffLL) return fail(ENC_ERR_UNSUPPORTED, "%s: more than 2^31-1 rows", name);
     if (variant >= ROW_VARIANTS) return fail(ENC_ERR_BAD_ARG, "%s: variant %d out of range", name, variant);
     // measured: RMSNorm bf16 [16384, 4096] is fastest with four times the minimum threads per row (97% of the copy
-    // bandwidth against 95%), LayerNorm with twice, softmax fp32 [4096, 1024] and [4096, 4096] with the minimum
-    if (variant < 0)
-        variant = OP == OP_SOFTMAX ? 0 : (OP == OP_RMSNORM && a.cols * (int64_t)sizeof(T) >= 4096 ? 6 : kAutoVariant);
+    // bandwidth against 95%), LayerNorm with twice, softmax fp32 [4096, 1024] and [4096, 4096] with the minimum.
+    // float32 rows of 4096 (16 KB): LayerNorm with the minimum and 256-thread CTAs (5.66 against 5.15 TB/s), RMSNorm
+    // with twice the minimum (6.2 against 5.1 TB/s).  Wide 16-bit softmax rows take four times the minimum, 32 elements
+    // per thread with the exponentials kept in registers (4.9 against 3.8 TB/s with the minimum and recomputation).
+    if (variant < 0) {
+        if (OP == OP_SOFTMAX) variant = sizeof(T) == 2 && a.cols > 2048 ? 6 : 0;
+        else if (OP == OP_LAYERNORM) variant = sizeof(T) == 4 && a.cols >= 2048 ? 1 : kAutoVariant;
+        else variant = sizeof(T) == 4 ? 3 : (a.cols * (int64_t)sizeof(T) >= 4096 ? 6 : kAutoVariant);
+    }
     const bool pipe = variant >= 12;
     const int shift = (variant % 12) / 3;
     int cta = 128 << (variant % 3);
