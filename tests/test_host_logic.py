@@ -159,7 +159,7 @@ def test_config_round_trip_and_identity():
     c = enceladus.Config({"BM": 128, "BN": 256, "BK": 64}, num_warps=8, dot_warps=[4, 2], variant=2)
     assert c.dot_warps == (4, 2)
     d = enceladus.Config.from_json(json.loads(json.dumps(c.to_json())))
-    assert d == c and d._identity() == c._identity()
+    assert d == c and d.tag() == c.tag()
     assert c.launch_options() == {"num_warps": 8, "dot_warps": (4, 2), "variant": 2}
     assert "variant=2" in str(c)
     with pytest.raises(ValueError, match="dot_backend"):
@@ -180,15 +180,8 @@ def test_configs_lists():
         configs.attention_configs("float16", 48)
 
 
-class _Recorder:
-    """Stands in for a JITFunction-backed kernel so tuning can run without a device."""
-
-    def __init__(self):
-        self.calls = []
-
-
 def _tuner(monkeypatch, tmp_path, times, tolerance=0.01):
-    """An autotuner over a fake kernel whose per-variant time is scripted by `times`."""
+    """An autotuner over a stand-in kernel whose per-variant launch time is scripted by `times` (milliseconds)."""
     monkeypatch.setenv("ENCELADUS_CACHE_DIR", str(tmp_path))
 
     @enceladus.jit
@@ -200,17 +193,17 @@ def _tuner(monkeypatch, tmp_path, times, tolerance=0.01):
     configs = [enceladus.Config({"BLOCK": 256 << i}, variant=i) for i in range(len(times))]
     state = {"current": None}
 
-    def fake_bench(fn, warmup_ms=50.0, rep=20, return_mode="median", flush_l2=False):
-        fn()
-        t = times[calls[-1]]
-        return [t] * rep if return_mode == "all" else t
+    def scripted(launch, count):  # stands in for the CUDA-event timer: runs the launches, reports the script's time
+        out = []
+        for _ in range(count):
+            launch()
+            out.append(times[calls[-1]])
+        return out
 
-    import enceladus_b200.testing as testing
-
-    monkeypatch.setattr(testing, "do_bench", fake_bench)
-    monkeypatch.setattr(autotuner, "_device_view", lambda v: v)
-    monkeypatch.setattr(autotuner.Autotuner, "_arch", lambda self: "test-arch")
-    tuned = enceladus.autotune(configs=configs, key=["n"], tolerance=tolerance)(add_kernel)
+    monkeypatch.setattr(autotuner, "time_launches", scripted)
+    monkeypatch.setattr(autotuner, "on_device", lambda v: v)
+    monkeypatch.setattr(autotuner, "device_tag", lambda: "test-arch")
+    tuned = enceladus.autotune(configs=configs, key=["n"], tolerance=tolerance, warmup_ms=0)(add_kernel)
     return tuned, calls, configs, state
 
 
@@ -233,7 +226,7 @@ def test_autotuner_picks_the_fastest_outside_tolerance_and_persists(monkeypatch,
     files = list(Path(tmp_path).rglob("test-arch.json"))
     assert len(files) == 1
     saved = json.loads(files[0].read_text())
-    assert next(iter(saved.values()))["variant"] == 1
+    assert next(iter(saved["results"].values()))["config"]["variant"] == 1 and "library" in saved
     # a new tuner for the same kernel reads the file and does not benchmark
     tuned2, calls2, configs2, _ = _tuner(monkeypatch, tmp_path, [9.0, 9.0, 9.0])
     tuned2[(1,)](x, x, x, 8)
@@ -242,6 +235,29 @@ def test_autotuner_picks_the_fastest_outside_tolerance_and_persists(monkeypatch,
     y = np.zeros(16, np.float32)
     tuned2[(1,)](y, y, y, 16)
     assert len(calls2) > 2
+    # a saved winner is an index into the library's variant list: another list (another digest) makes the file stale
+    monkeypatch.setattr(autotuner, "library_digest", lambda jit: "another-build")
+    tuned3, calls3, configs3, _ = _tuner(monkeypatch, tmp_path, [1.0, 3.0, 3.0])
+    tuned3[(1,)](x, x, x, 8)
+    assert len(calls3) > 1 and tuned3.config_for(x, x, x, 8) is configs3[0]
+
+
+def test_autotuner_drops_candidates_that_are_out_of_reach_and_restores_arguments(monkeypatch, tmp_path):
+    import torch
+
+    tuned, calls, configs, _ = _tuner(monkeypatch, tmp_path, [1.0, 5.0, 1.02, 0.97])
+    tuned.restore_value, tuned.reset_to_zero = ["x_ptr"], ["out_ptr"]
+    x, out = torch.arange(8, dtype=torch.float32), torch.ones(8)
+    seen_x = []
+    hooked = configs[3]
+    hooked.pre_hook = lambda args: seen_x.append(args["x_ptr"].clone())
+    monkeypatch.setattr(tuned.jit, "run", lambda *a, grid, **kw: (calls.append(kw.get("variant")), a[0].add_(1), a[2].add_(1)))
+    tuned[(1,)](x, x, out, 8)
+    # variant 1 is five times slower: it is timed in the first pass only; the close ones race to the end
+    assert calls.count(1) < calls.count(0) and calls.count(2) == calls.count(0)
+    assert tuned.config_for(x, x, out, 8) is hooked  # 0.97 beats 1.0 by more than the 1% tolerance
+    assert all(torch.equal(v, torch.arange(8, dtype=torch.float32)) for v in seen_x)  # restored before every launch
+    assert set(tuned.timings[next(iter(tuned.timings))]) == {str(c) for c in configs}
 
 
 def test_autotuner_skips_failing_configs(monkeypatch, tmp_path):
