@@ -655,15 +655,24 @@ __global__ void __launch_bounds__(256) sum_partials_kernel(const TIn *in, int64_
     const int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     const int64_t nvec = aligned16(in) ? n / PER : 0;
     const uint4 *v = reinterpret_cast<const uint4 *>(in);
-    int64_t i = tid;
-    for (; i + 3 * stride < nvec; i += 4 * stride) {
-        const uint4 a = ld_stream(v + i), b = ld_stream(v + i + stride), c = ld_stream(v + i + 2 * stride), d = ld_stream(v + i + 3 * stride);
-        s0 += sum_vec16<TIn, Acc>(a);
-        s1 += sum_vec16<TIn, Acc>(b);
-        s2 += sum_vec16<TIn, Acc>(c);
-        s3 += sum_vec16<TIn, Acc>(d);
+    // A CTA reads slabs of 8 x 256 consecutive vectors (32 KB): eight loads in flight per thread, each a fully
+    // coalesced 4 KB row of the slab, slabs dealt round-robin to the CTAs.
+    constexpr int U = 8;
+    const int64_t slab = (int64_t)U * blockDim.x, nslabs = nvec / slab;
+    for (int64_t sl = blockIdx.x; sl < nslabs; sl += gridDim.x) {
+        const uint4 *p = v + sl * slab + threadIdx.x;
+        uint4 q[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u) q[u] = ld_stream(p + u * blockDim.x);
+#pragma unroll
+        for (int u = 0; u < U; u += 4) {
+            s0 += sum_vec16<TIn, Acc>(q[u]);
+            s1 += sum_vec16<TIn, Acc>(q[u + 1]);
+            s2 += sum_vec16<TIn, Acc>(q[u + 2]);
+            s3 += sum_vec16<TIn, Acc>(q[u + 3]);
+        }
     }
-    for (; i < nvec; i += stride) s0 += sum_vec16<TIn, Acc>(ld_stream(v + i));
+    for (int64_t i = nslabs * slab + tid; i < nvec; i += stride) s0 += sum_vec16<TIn, Acc>(ld_stream(v + i));
     for (int64_t j = nvec * PER + tid; j < n; j += stride) s1 += to_acc<Acc, TIn>(in[j]);
     Acc s = (s0 + s1) + (s2 + s3);
 #pragma unroll
@@ -860,7 +869,7 @@ int launch_sum(const void *in, void *total, int64_t n, void *stream) {
     using Acc = typename AccOf<TIn>::type;
     cudaStream_t st = as_stream(stream);
     int64_t grid = (int64_t)device_props().sm_count * 8;
-    const int64_t need = cdiv(n > 0 ? n : 1, 256 * 4 * (16 / (int64_t)sizeof(TIn)));
+    const int64_t need = cdiv(n > 0 ? n : 1, 256 * 8 * (16 / (int64_t)sizeof(TIn)));
     if (grid > need) grid = need;
     Acc *partials = (Acc *)scratch_get((size_t)grid * sizeof(Acc), stream);
     if (!partials) return fail(ENC_ERR_NO_MEMORY, "enc_sum: cannot allocate scratch");

@@ -72,6 +72,32 @@ def test_matmul_strided_views_and_unaligned_fallback(oracle):
     assert_close(host(ops.matmul_bias_gelu(torch_of(a2), torch_of(b2), torch_of(bias2))), oracle.matmul_bias_gelu(a2, b2, bias2, 32))
 
 
+@pytest.mark.parametrize("dt", [F16, BF16], ids=str)
+@pytest.mark.parametrize("mnk", [(513, 513, 513), (257, 130, 71), (129, 1000, 333), (64, 65, 2049), (1, 7, 9)], ids=str)
+def test_matmul_operands_tma_cannot_describe(oracle, dt, mnk):
+    """Odd leading dimensions (the reference's 513^3 shape among them) and bases that are not 16-byte aligned: the
+    tensor-core kernel's loader warps fill the swizzled stages themselves; every tile variant, ragged edges in all
+    three dimensions, fused and plain."""
+    m, n, k = mnk
+    a, b, bias = operands(np.random.default_rng(m * n + k), m, n, k, dt)
+    want = oracle.matmul_bias_gelu(a, b, bias, bk=64)
+    at, bt, biast = torch_of(a), torch_of(b), torch_of(bias)
+    for v in [None, *range(N.num_variants(N.K_MATMUL))]:
+        c = enceladus.new_empty(at, (m, n))
+        ops.matmul_bias_gelu_kernel[(enceladus.cdiv(n, 64), enceladus.cdiv(m, 128))](at, bt, biast, c, m, n, k, k, n, n, BM=128, BN=64,
+                                                                                   BK=64, variant=v)
+        assert_close(host(c), want, what=f"variant {v}")
+    assert_close(host(ops.matmul_desc(at, bt)), oracle.matmul(a, b, 64))
+    # aligned leading dimensions but a base shifted by one element (2 bytes)
+    import torch
+
+    flat = torch.zeros(m * (k + 8) + 1, dtype=at.dtype, device="cuda")
+    shifted = flat[1:].view(m, k + 8)[:, :k]
+    shifted.copy_(at)
+    assert_close(host(ops.matmul_bias_gelu(shifted, bt, biast)), want)
+    enceladus.synchronize()
+
+
 def test_matmul_config3_rows_sampled(oracle):
     """Full-size fused matmul (8192^3 fp16): a sample of rows against the oracle, all rows against linearity."""
     import torch
