@@ -13,9 +13,8 @@
  *   - plain pointers and sizes only; every pointer is a DEVICE pointer on the current CUDA device
  *     unless the parameter name ends in `_host`;
  *   - the caller owns all buffers.  The library itself owns, per device: a 256-byte status block (bounded
- *     device-side waits report there), the tile-descriptor scratch of enc_cumsum / enc_sum (see enc_cumsum)
- *     and a workspace for split-K partial sums of enc_matmul (see enc_matmul); all are allocated on first
- *     use and freed at exit;
+ *     device-side waits report there) and the tile-descriptor scratch of enc_cumsum / enc_sum (see
+ *     enc_cumsum); both are allocated on first use and freed at exit.  No other entry point allocates;
  *   - `stream` is a cudaStream_t / CUstream passed as void* (NULL = the legacy default stream); work
  *     is enqueued and the call returns without synchronising, like fr_stream_dispatch;
  *   - the return value is an enc_status; on failure enc_last_error() holds a message for the calling
@@ -190,7 +189,10 @@ int enc_scan_offset(const void *totals, int count, int index, void *offset, int 
  * stride, float32 accumulation on tcgen05 tensor cores (float32 operands: CUDA cores), C in the operand dtype.
  * epilogue 0: identity.  epilogue 1: t = acc + bias[n]; 0.5*t*(1+erf(t*0.70710677f)).
  * Out-of-range tile elements read as zero and are not stored (descriptor semantics,
- * src/enceladus/language/ops.py:495-514).  dtype: ENC_F16 | ENC_BF16 | ENC_F32.
+ * src/enceladus/language/ops.py:495-514).  dtype: ENC_F16 | ENC_BF16 | ENC_F32.  Operands need no alignment:
+ * 16-byte aligned bases and leading dimensions that are multiples of 8 are fetched by TMA, anything else (the
+ * reference's 513^3 shape, benchmarks/bench_matmul.py:30) by loader warps inside the same tensor-core kernel;
+ * nothing is copied or allocated.
  * Replaces matmul_bias_gelu_kernel[(cdiv(N,BN),cdiv(M,BM))](a, b, bias, c, M, N, K, lda, ldb, ldc, BM, BN, BK)
  *                                                                                    examples/07_matmul_fused.py:17-48
  * and matmul_desc_kernel                                                             examples/04_matmul.py:21-63 */
