@@ -656,10 +656,13 @@ __global__ void __launch_bounds__(256) sum_partials_kernel(const TIn *in, int64_
     const int64_t nvec = aligned16(in) ? n / PER : 0;
     const uint4 *v = reinterpret_cast<const uint4 *>(in);
     // A CTA reads slabs of 8 x 256 consecutive vectors (32 KB): eight loads in flight per thread, each a fully
-    // coalesced 4 KB row of the slab, slabs dealt round-robin to the CTAs.
+    // coalesced 4 KB row of the slab, slabs dealt round-robin to the CTAs.  The slabs are walked from the END of the
+    // array towards its beginning: the scan that follows this pass in the multi-GPU recipe starts at the beginning,
+    // which is then what L2 still holds.
     constexpr int U = 8;
     const int64_t slab = (int64_t)U * blockDim.x, nslabs = nvec / slab;
-    for (int64_t sl = blockIdx.x; sl < nslabs; sl += gridDim.x) {
+    for (int64_t it = blockIdx.x; it < nslabs; it += gridDim.x) {
+        const int64_t sl = nslabs - 1 - it;
         const uint4 *p = v + sl * slab + threadIdx.x;
         uint4 q[U];
 #pragma unroll
