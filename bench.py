@@ -53,18 +53,18 @@ ROTATE_BYTES = 1 << 30  # total size of the rotating buffer sets for workloads s
 # workloads were captured at 2^27 elements (few GB on the device under the profiler) and are scaled by
 # the element count: their traffic is proportional to it.
 NCU_TRAFFIC: dict[str, float | None] = {
-    "layernorm_bf16_16384x4096": 216_550_656,       # profiles/layernorm.md
-    "rmsnorm_bf16_16384x4096": 217_106_176,         # profiles/rmsnorm.md
-    "softmax_f32_4096x1024": 16_793_600,            # profiles/softmax.md (the 16 MiB output stays in L2)
+    "layernorm_bf16_16384x4096": 216_842_496,       # profiles/layernorm.md
+    "rmsnorm_bf16_16384x4096": 218_600_192,         # profiles/rmsnorm.md
+    "softmax_f32_4096x1024": 16_793_856,            # profiles/softmax.md (the 16 MiB output stays in L2)
     "gelu_tanh_f32_2p28": 2_100_776_000,            # profiles/gelu.md
     "histogram_i32_2p30_uniform256": 8 * 540_655_616,   # profiles/hist_uniform256.md, captured at 2^27
     "histogram_i32_2p30_zipf4096": 8 * 540_067_328,     # profiles/hist_zipf4096.md, captured at 2^27
-    "cumsum_i32_2p30": 8 * 1_014_728_192,           # profiles/cumsum_i32.md, captured at 2^27
-    "cumsum_f32_2p28": 2 * 1_016_665_600,           # profiles/cumsum_f32.md, captured at 2^27
-    "matmul_bias_gelu_f16_8192x8192x8192": 1_109_306_624,   # profiles/matmul.md
+    "cumsum_i32_2p30": 8 * 1_015_634_688,           # profiles/cumsum_i32.md, captured at 2^27
+    "cumsum_f32_2p28": 2 * 1_015_431_168,           # profiles/cumsum_f32.md, captured at 2^27
+    "matmul_bias_gelu_f16_8192x8192x8192": 1_048_525_312,   # profiles/matmul.md
     "matmul_int8_8192x8192x8192": 571_891_712,              # profiles/matmul_int8.md
-    "attention_bf16_8x32x4096x128_full": 1_052_659_968,     # profiles/attention_full.md
-    "attention_bf16_8x32x4096x128_causal": 1_057_350_912,   # profiles/attention_causal.md
+    "attention_bf16_8x32x4096x128_full": 1_056_008_704,     # profiles/attention_full.md
+    "attention_bf16_8x32x4096x128_causal": 1_056_456_448,   # profiles/attention_causal.md
 }
 
 USE_GRAPH = True
