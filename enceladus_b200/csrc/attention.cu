@@ -986,9 +986,12 @@ attention_ts64_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
 //   producer       loads the next item's Q tiles as soon as the score products of the current item have read them
 //                  (q_empty, committed behind the last score MMA) and keeps the K / V rings full across the seam;
 //   score issuers  issue S(0), S(1) of the next item while the softmax warps are still in the epilogue;
-//   P V issuer     starts the next item's accumulation once the softmax warps have pulled O out of tensor memory
-//                  (o_empty); o_full is per tile, so with a causal mask the upper tile's epilogue overlaps the
-//                  lower tile's last two key blocks.
+//   P V issuer     starts the next item's accumulation once both softmax warpgroups have pulled O out of tensor memory
+//                  (o_empty, waited for once per item, outside its block loop; o_full is committed once per item
+//                  behind the last product).  Its block loop is the one-shot kernel's, with the buffer parity taken
+//                  from a per-tile block count carried across items: per-tile completion barriers and tests for an
+//                  item's first and last block inside that loop were measured and cost 10% of the kernel, because
+//                  every instruction this thread spends between two products delays the tensor core.
 // Schedule: item k = (slice k / n_qb, query block perm[k % n_qb]); CTA c takes k = r G + c in even rounds r and
 // k = r G + (G-1-c) in odd ones.  Consecutive items share a slice, so the CTAs of a round read a few slices' K / V
 // from L2 as the one-shot grid does.  For causal launches `perm` pairs the query blocks so that the two items a
@@ -1060,9 +1063,9 @@ attention_p64_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
     uint64_t *s_full = v_empty + STAGES;  // [tile * 2 + buffer]
     uint64_t *p_full = s_full + 4;
     uint64_t *pv_done = p_full + 4;
-    uint64_t *o_full = pv_done + 4;       // [2]
-    uint64_t *o_empty = o_full + 2;       // [2]
-    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(o_empty + 2);
+    uint64_t *o_full = pv_done + 4;       // both accumulators complete (committed behind an item's last product)
+    uint64_t *o_empty = o_full + 1;       // both softmax warpgroups have pulled their accumulator out of tensor memory
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(o_empty + 1);
     volatile uint32_t *abort = tmem_slot + 1;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -1073,8 +1076,6 @@ attention_p64_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
         for (int t = 0; t < 2; ++t) {
             mbar_init(&q_full[t], 1);
             mbar_init(&q_empty[t], 1);
-            mbar_init(&o_full[t], 1);
-            mbar_init(&o_empty[t], 128);
         }
         for (int s = 0; s < STAGES; ++s) {
             mbar_init(&k_full[s], 1);
@@ -1087,6 +1088,8 @@ attention_p64_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
             mbar_init(&p_full[i], 128);
             mbar_init(&pv_done[i], 1);
         }
+        mbar_init(o_full, 1);
+        mbar_init(o_empty, 256);
         *abort = 0;
         fence_barrier_init();
         prefetch_tensormap(&tm_q);
@@ -1161,7 +1164,7 @@ attention_p64_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
             const uint32_t k_lo = smem_desc_lo(smem_u32(smem + L::K_OFF), 16);
             const uint32_t s_tmem = tmem_base + t * 128;
             uint32_t stage = 0, phase = 0;
-            uint32_t cs = 0;   // score blocks of this tile issued so far, over all items
+            uint32_t base = 0;  // score blocks of this tile issued in earlier items
             uint32_t n_it = 0;
             bool ok = true;
             for (int r = 0; r < rounds; ++r) {
@@ -1182,9 +1185,9 @@ attention_p64_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
                     ok = mbar_wait(&k_full[stage], phase, abort);
                     if (!ok) break;
                     if (j < my_nkv) {
-                        const uint32_t b = cs & 1;
-                        // buffer b held S, then P, of this tile's block cs - 2: free once that P V has completed
-                        if (cs >= 2) ok = mbar_wait(&pv_done[t * 2 + b], ((cs - 2) >> 1) & 1, abort);
+                        const uint32_t c = base + j, b = c & 1;
+                        // buffer b held S, then P, of this tile's block c - 2: free once that P V has completed
+                        if (c >= 2) ok = mbar_wait(&pv_done[t * 2 + b], ((c - 2) >> 1) & 1, abort);
                         if (!ok) break;
                         tc_fence_after();
                         const uint32_t kb = k_lo + stage * (L::TILE >> 4);
@@ -1194,12 +1197,12 @@ attention_p64_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
                             tc_mma_f16_halves(d_tmem, q_lo + (((kk >> 2) * (BM * 128) + (kk & 3) * 32) >> 4), desc_hi,
                                               kb + (((kk >> 2) * (BNK * 128) + (kk & 3) * 32) >> 4), desc_hi, idesc_s, kk != 0);
                         tc_commit(&s_full[t * 2 + b]);
-                        ++cs;
                     }
                     tc_commit(&k_empty[stage]);
                     if (++stage == STAGES) { stage = 0; phase ^= 1; }
                 }
                 if (ok) tc_commit(&q_empty[t]);  // arrives when every score product of this item has read Q_t
+                base += my_nkv;
             }
         } else if (warp == 3 && lane == 0) {
             // ---------------- P V issuer, both tiles in turn ----------------
@@ -1207,10 +1210,11 @@ attention_p64_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
             constexpr uint32_t desc_hi = smem_desc_hi_sw128(1024);
             const uint32_t v_lo = smem_desc_lo(smem_u32(smem + L::V_OFF), BNK * 128);
             uint32_t stage = 0, phase = 0;
-            // per-tile counters as scalars (an array indexed by the tile lands in local memory, and a reload in front of
-            // every product is a few hundred cycles on the thread that feeds the tensor core)
-            uint32_t cp0 = 0, cp1 = 0;    // P blocks consumed per tile, over all items
-            uint32_t n_o0 = 0, n_o1 = 0;  // items with work per tile
+            // This thread feeds the tensor core: the loop below is kept instruction for instruction as lean as the one-shot
+            // kernel's (measured: testing for the first and the last block of an item inside it, and per-tile completion
+            // barriers, cost 10% of the whole kernel).  What an item needs beyond that happens once, outside the loop.
+            uint32_t base0 = 0, base1 = 0;  // P blocks consumed per tile in earlier items
+            uint32_t n_o = 0;               // items finished
             bool ok = true;
             for (int r = 0; r < rounds; ++r) {
                 int bh, qb;
@@ -1218,35 +1222,34 @@ attention_p64_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
                 int64_t m0;
                 int nkv_t[2], nkv;
                 item_extent(a, qb, m0, nkv_t, nkv);
-                const int nkv0 = nkv_t[0], nkv1 = nkv_t[1];
+                // the first product of an item overwrites O: the previous item's epilogue must have read both accumulators
+                ok = mbar_wait(o_empty, (n_o & 1) ^ 1, abort);
+                if (!ok) continue;
                 for (int j = 0; j < nkv && ok; ++j) {
                     ok = mbar_wait(&v_full[stage], phase, abort);
                     if (!ok) break;
                     const uint32_t vb = v_lo + stage * (L::TILE >> 4);
-                    auto product = [&](const int t, const int my_nkv, uint32_t &cp, uint32_t &n_o) -> bool {
-                        if (j >= my_nkv) return true;
-                        const uint32_t b = cp & 1;
-                        if (!mbar_wait(&p_full[t * 2 + b], (cp >> 1) & 1, abort)) return false;
-                        // the first product of an item overwrites O_t: the previous item's epilogue must have read it
-                        if (j == 0 && !mbar_wait(&o_empty[t], (n_o & 1) ^ 1, abort)) return false;
+#pragma unroll
+                    for (int t = 0; t < 2; ++t) {
+                        if (j >= nkv_t[t]) continue;
+                        const uint32_t c = (t == 0 ? base0 : base1) + j;
+                        ok = mbar_wait(&p_full[t * 2 + (c & 1)], (c >> 1) & 1, abort);
+                        if (!ok) break;
                         tc_fence_after();
-                        const uint32_t p_tmem = tmem_base + t * 128 + b * BNK;
+                        const uint32_t p_tmem = tmem_base + t * 128 + (c & 1) * BNK;
 #pragma unroll
                         for (int kk = 0; kk < BNK / 16; ++kk)  // 16 keys = 8 packed columns of P, 16 rows = 2048 bytes of V
                             tc_mma_f16_ts_halves(tmem_base + 256 + t * 128, p_tmem + kk * 8, vb + kk * (2048 >> 4), desc_hi, idesc_o, (j | kk) != 0);
-                        tc_commit(&pv_done[t * 2 + b]);
-                        ++cp;
-                        if (j == my_nkv - 1) {
-                            tc_commit(&o_full[t]);
-                            ++n_o;
-                        }
-                        return true;
-                    };
-                    ok = product(0, nkv0, cp0, n_o0) && product(1, nkv1, cp1, n_o1);
+                        tc_commit(&pv_done[t * 2 + (c & 1)]);
+                    }
                     if (!ok) break;
                     tc_commit(&v_empty[stage]);
                     if (++stage == STAGES) { stage = 0; phase ^= 1; }
                 }
+                if (ok) tc_commit(o_full);
+                base0 += nkv_t[0];
+                base1 += nkv_t[1];
+                ++n_o;
             }
         }
     } else {
@@ -1258,7 +1261,7 @@ attention_p64_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
         const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
         const uint32_t t_s = tmem_base + lane_addr + t * 128;
         const uint32_t t_o = tmem_base + lane_addr + 256 + t * 128;
-        uint32_t cs = 0, n_o = 0;
+        uint32_t base = 0, n_o = 0;  // score blocks of this tile in earlier items; items finished
         bool ok = true;
         for (int r0 = 0; r0 < rounds; ++r0) {
             int bh, qb;
@@ -1273,8 +1276,8 @@ attention_p64_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
             const int last = a.causal && row < seq ? row : seq - 1;  // last key this row sees
             float m_ref = -INFINITY, l = 0.0f;
             for (int j = 0; j < my_nkv && ok; ++j) {
-                const uint32_t b = cs & 1;
-                ok = mbar_wait(&s_full[t * 2 + b], (cs >> 1) & 1, abort);
+                const uint32_t c = base + j, b = c & 1;
+                ok = mbar_wait(&s_full[t * 2 + b], (c >> 1) & 1, abort);
                 if (!ok) break;
                 tc_fence_after();
                 const int n0 = j * BNK;
@@ -1288,7 +1291,7 @@ attention_p64_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
                 softmax_row_lim<2, kPolyPairs>(sv, a.qk_scale, need_mask, last - n0, m_ref, l, alpha, rescale);
                 if (j > 0 && __any_sync(0xffffffffu, rescale)) {
                     // O_t must be quiescent: P_t(j-1) V complete (P_t(j) V is not issued before this thread's arrival below)
-                    ok = mbar_wait(&pv_done[t * 2 + (b ^ 1)], ((cs - 1) >> 1) & 1, abort);
+                    ok = mbar_wait(&pv_done[t * 2 + (b ^ 1)], ((c - 1) >> 1) & 1, abort);
                     if (!ok) break;
                     tc_fence_after();
 #pragma unroll 1
@@ -1311,34 +1314,34 @@ attention_p64_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
                 tmem_st_wait();
                 tc_fence_before();
                 mbar_arrive(&p_full[t * 2 + b]);
-                ++cs;
             }
             // ---- epilogue: O_t / l; the accumulator is handed back as soon as its last columns are in registers ----
-            if (ok && my_nkv > 0) {
-                ok = mbar_wait(&o_full[t], n_o & 1, abort);
-                if (!ok) continue;
-                ++n_o;
-                tc_fence_after();
-                T *o = reinterpret_cast<T *>(a.o) + (int64_t)bh * a.stride_h + (int64_t)row * a.stride_m;
+            base += my_nkv;
+            ok = ok && mbar_wait(o_full, n_o & 1, abort);  // (every thread of both warpgroups waits and arrives, work or not)
+            if (!ok) continue;
+            ++n_o;
+            tc_fence_after();
+            T *o = reinterpret_cast<T *>(a.o) + (int64_t)bh * a.stride_h + (int64_t)row * a.stride_m;
 #pragma unroll 1
-                for (int c0 = 0; c0 < D; c0 += 32) {
-                    uint32_t v[32];
+            for (int c0 = 0; c0 < D; c0 += 32) {
+                uint32_t v[32];
+                if (my_nkv > 0) {
                     tmem_ld_32x32(t_o + c0, v);
                     tmem_ld_wait();
-                    if (c0 + 32 == D) {
-                        tc_fence_before();
-                        mbar_arrive(&o_empty[t]);
-                    }
-                    if (row < seq) {
-                        float f[32];
-#pragma unroll
-                        for (int i = 0; i < 32; ++i) f[i] = __fdiv_rn(__uint_as_float(v[i]), l);
-#pragma unroll
-                        for (int i = 0; i < 4; ++i) *reinterpret_cast<uint4 *>(o + c0 + 8 * i) = Pack<T>::pack(f + 8 * i);
-                    }
                 }
-                if (a.lse && row < seq) a.lse[(int64_t)bh * a.seq + row] = (m_ref + log2f(l)) * LN2;
+                if (c0 + 32 == D) {
+                    tc_fence_before();
+                    mbar_arrive(o_empty);
+                }
+                if (my_nkv > 0 && row < seq) {
+                    float f[32];
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) f[i] = __fdiv_rn(__uint_as_float(v[i]), l);
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) *reinterpret_cast<uint4 *>(o + c0 + 8 * i) = Pack<T>::pack(f + 8 * i);
+                }
             }
+            if (a.lse && my_nkv > 0 && row < seq) a.lse[(int64_t)bh * a.seq + row] = (m_ref + log2f(l)) * LN2;
         }
     }
 
@@ -1350,7 +1353,6 @@ attention_p64_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
         tmem_dealloc(tmem_base, TMEM_COLS);
     }
 }
-
 // ---- CUDA-core kernel: any head_dim <= 128, any of the three dtypes, any strides -------------------
 // One CTA of 128 threads per (batch*head, 16 query rows): 8 threads share a row and split head_dim.
 template <typename T>
@@ -1547,14 +1549,17 @@ int launch_attention(const void *q, const void *k, const void *v, AttnArgs args,
     if (!args.error) return fail(ENC_ERR_NO_MEMORY, "enc_attention_fwd: cannot allocate the device status word");
     if constexpr (sizeof(T) == 2) {
         if (variant < 0) {
-            // Two tiles per CTA once there are two tiles.  Measured on B200 (bf16/f16, D = 128 and 64): the one-shot grid
-            // (variant 3) is 5-12% faster than the persistent kernel wherever the hardware's own dynamic dispatch of CTAs
-            // balances well - many CTAs per SM, or at most one - because the persistent kernel's inner loops run slower (its
-            // code keeps more per-item state live next to the softmax registers), which its saved set-up time (about 5% of a
-            // 256-row item at 4096 keys) does not pay back.  The persistent kernel wins (by 20-26%) where dispatch order
-            // cannot balance: causal launches with between one and two items per SM, e.g. [1, 16, 4096, D].
+            // Two tiles per CTA once there are two tiles.  One-shot grid (variant 3) or persistent CTAs (variant 4), as measured
+            // on B200 (bf16/f16, D = 128 and 64, sequences 512 to 16384).  The persistent kernel saves the per-item set-up and
+            // balances causal work statically, but its inner loops still run about 5% slower than the one-shot kernel's, so it
+            // wins where items are short or uneven: causal launches up to 4096 keys (+3% at [8,32,4096,128], +9% at 2048, +13%
+            // at 512, +27-32% at [1,16,4096,D], where the hardware's dispatch order cannot balance 256 uneven CTAs over 148
+            // SMs) and non-causal launches up to 2048 keys (+1% to +13%).  It loses with long non-causal items (-5% at 4096
+            // keys, -14% at 16384), beyond 4096 keys causal (its balancing permutation covers 16 query blocks), and whenever
+            // there is at most one item per SM.
             const int64_t items = cdiv(args.seq, 2 * BM) * bh, sms = device_props().sm_count;
-            variant = args.seq <= BM ? 1 : (args.causal && items > sms && items <= 2 * sms && args.seq >= 12 * 2 * BM) ? 4 : 3;
+            const bool persistent = items > sms && args.seq <= (args.causal ? 4096 : 2048);
+            variant = args.seq <= BM ? 1 : persistent ? 4 : 3;
         }
         if (variant == 4) return d == 128 ? launch_persistent<T, 128, 5>(q, k, v, args, bh, st) : launch_persistent<T, 64, 6>(q, k, v, args, bh, st);
         if (d == 128) {
