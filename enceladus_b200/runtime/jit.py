@@ -362,7 +362,7 @@ def launch(ad, bound: dict[str, Any], grid: tuple[int, int, int], variant: int, 
 
 PIPELINE_MIN_BYTES = 16 << 20   # below this much partitioned host data a launch is staged in one piece
 PIPELINE_PIECE_BYTES = 32 << 20  # target size of a piece, inputs and outputs together (measured best of 16-128 MB)
-PIPELINE_STREAMS = 3
+PIPELINE_STREAMS = 2  # one per direction of the link
 _side_streams: dict[int, list[Any]] = {}
 
 
@@ -399,52 +399,71 @@ def _pipeline_plan(ad, bound: dict[str, Any], grid: tuple[int, int, int], host_n
 
 
 def _launch_pipelined(ad, bound, grid, variant, jf, host_names, sp, pieces) -> None:
-    """Stages, runs and copies back one piece after the other on a few side streams, then waits for all of
-    them: the launch is complete when this returns, as the one-piece path is."""
+    """Stages, runs and copies back one piece after the other, then waits for all of it: the launch is complete
+    when this returns, as the one-piece path is.
+
+    Two side streams, one per direction of the link: copies in and the kernels on the first, copies out on the
+    second, an event per piece between them.  Copies of one direction then run one after the other in piece
+    order, so the first piece's kernel starts after one piece's transfer and the link is busy both ways from
+    then on.  (Measured on B200, LayerNorm bf16 [16384, 4096] from pinned memory: 3.13 ms against 3.68 ms with
+    whole pieces dealt round-robin to three streams, where the copies in of neighbouring pieces shared the
+    link and every kernel started late; smaller pieces at both ends of the schedule did not pay, each extra
+    piece costs about 50 us.)"""
     torch = interop._torch()
     cur = torch.cuda.current_stream()
     di = torch.cuda.current_device()
     streams = _side_streams.get(di)
     if streams is None:
         streams = _side_streams[di] = [torch.cuda.Stream() for _ in range(PIPELINE_STREAMS)]
+    s_in, s_out = streams
     staged = interop.Staged()
     shared = dict(bound)
-    for name in host_names:
-        if name not in sp.arrays:
-            shared[name] = staged.to_device(name, bound[name], False)
     ready = cur.record_event()
+    s_in.wait_event(ready)
+    s_out.wait_event(ready)
     extents = ad.extents(bound, grid) if ad.extents is not None else {}
     flat = {name: bound[name].reshape(-1) for name in sp.arrays}
     dense = {name: extents.get(name) == bound[name].size for name in sp.arrays}
-    late: list[tuple[Any, Any]] = []
+    # An output in pageable host memory cannot be copied out piece by piece: such a copy blocks the host until
+    # the stream gets there.  It is staged whole, the pieces write slices of it, and one copy follows at the end.
+    whole: dict[str, Any] = {}
     try:
-        for i, (u0, n) in enumerate(pieces):
-            st = streams[i % len(streams)]
-            if i < len(streams):
-                st.wait_event(ready)
-            with torch.cuda.stream(st):
+        with torch.cuda.stream(s_in):
+            for name in host_names:
+                if name not in sp.arrays:
+                    shared[name] = staged.to_device(name, bound[name], False)
+            for name in sp.arrays:
+                if name in ad.outputs and not interop._np_as_torch_view(flat[name]).is_pinned():
+                    whole[name] = staged.to_device(name, flat[name], True, overwritten=dense[name])
+        for u0, n in pieces:
+            with torch.cuda.stream(s_in):
                 piece = dict(shared)
                 piece.update(sp.rebind(n))
                 views = []
                 for name, per in sp.arrays.items():
-                    host = flat[name][u0 * per : min((u0 + n) * per, flat[name].size)]
+                    lo, hi = u0 * per, min((u0 + n) * per, flat[name].size)
+                    if name in whole:
+                        piece[name] = whole[name][lo:hi]
+                        continue
+                    host = flat[name][lo:hi]
                     written = name in ad.outputs
                     piece[name] = staged.to_device(name, host, written, overwritten=dense[name])
                     if written:
+                        piece[name].record_stream(s_out)  # allocated on s_in, read by the copy out on s_out
                         views.append((piece[name], host))
-                ad.fn(piece, sp.grid(n), variant, int(st.cuda_stream))
+                ad.fn(piece, sp.grid(n), variant, int(s_in.cuda_stream))
+                done = s_in.record_event()
+            with torch.cuda.stream(s_out):
+                s_out.wait_event(done)
                 for d, host in views:
-                    hv = interop._np_as_torch_view(host)
-                    if hv.is_pinned():
-                        hv.copy_(d, non_blocking=True)
-                    else:  # a copy into pageable memory blocks the host until the stream gets there: do it last
-                        late.append((hv, d))
+                    interop._np_as_torch_view(host).copy_(d, non_blocking=True)
                     staged.d2h_bytes += host.nbytes
     finally:
         for st in streams:
             st.synchronize()
-    for hv, d in late:
-        hv.copy_(d)
+    for name, d in whole.items():
+        interop._np_as_torch_view(flat[name]).copy_(d)
+        staged.d2h_bytes += flat[name].nbytes
     staged.writeback.clear()
     if jf is not None:
         jf.last_launch = {"h2d_bytes": staged.h2d_bytes, "d2h_bytes": staged.d2h_bytes, "variant": variant,
