@@ -329,7 +329,9 @@ def workloads(scale: float = 1.0, shard: tuple[int, int] | None = None):
 
                 dist.all_reduce(want)
                 dist.all_reduce(total)
-            return bool((s[1].long() == want).all()) and int(s[1].long().sum()) == int(total)
+            # the bins are int32 and wrap like the reference's (hist = new_zeros(int32) + atomic_add): eight ranks' worth
+            # of the Zipf tail bin is 3.5e9 counts, so the comparison is modulo 2^32
+            return bool((s[1] == want.to(torch.int32)).all()) and (int(s[1].long().sum()) - int(total)) % (1 << 32) == 0
 
         return dict(name=f"histogram_i32_2p30_{kind}", kernel="histogram", jit=ops.histogram_kernel, unit="GB/s", bound="hbm", dtype="i32",
                     work=n * 4, set_bytes=n * 4, make=make, run=run, verify=verify, sets=1,
