@@ -23,9 +23,9 @@ class Split:
     """How a launch can be cut into independent pieces (rows, elements, M-blocks, (batch, head) slices).
 
     Used for NumPy arguments only: the launcher stages, runs and copies back one piece after the other on
-    a few streams, so that the host-to-device copy of piece i+1, the kernel of piece i and the
-    device-to-host copy of piece i-1 overlap (PCIe carries both directions at once).  Arrays that are not
-    listed are shared by all pieces and staged once.
+    two streams (copies in and kernels on one, copies out on the other), so that the host-to-device copy
+    of piece i+1 and the device-to-host copy of piece i overlap (PCIe carries both directions at once).
+    Arrays that are not listed are shared by all pieces and staged once.
     """
 
     units: int                                   # independent units in the launch
