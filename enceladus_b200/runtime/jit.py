@@ -392,7 +392,7 @@ def _pipeline_plan(ad, bound: dict[str, Any], grid: tuple[int, int, int], host_n
         return None
     pieces = int(max(2, min(32, total // PIPELINE_PIECE_BYTES)))
     per_piece = -(-sp.units // pieces)
-    per_piece = -(-per_piece // align) * align
+    per_piece = int(-(-per_piece // align) * align)  # (align is a NumPy integer)
     if per_piece >= sp.units:
         return None
     return sp, [(u0, min(per_piece, sp.units - u0)) for u0 in range(0, sp.units, per_piece)]
@@ -435,6 +435,7 @@ def _launch_pipelined(ad, bound, grid, variant, jf, host_names, sp, pieces) -> N
             for name in sp.arrays:
                 if name in ad.outputs and not interop._np_as_torch_view(flat[name]).is_pinned():
                     whole[name] = staged.to_device(name, flat[name], True, overwritten=dense[name])
+        before = None
         for u0, n in pieces:
             with torch.cuda.stream(s_in):
                 piece = dict(shared)
@@ -451,6 +452,9 @@ def _launch_pipelined(ad, bound, grid, variant, jf, host_names, sp, pieces) -> N
                     if written:
                         piece[name].record_stream(s_out)  # allocated on s_in, read by the copy out on s_out
                         views.append((piece[name], host))
+                if sp.chain is not None:
+                    sp.chain(piece, before)
+                    before = piece
                 ad.fn(piece, sp.grid(n), variant, int(s_in.cuda_stream))
                 done = s_in.record_event()
             with torch.cuda.stream(s_out):

@@ -32,6 +32,10 @@ class Split:
     arrays: dict[str, int]                       # partitioned array -> elements per unit in its flat view
     grid: Callable[[int], tuple[int, int, int]]  # units in a piece -> grid of its launch
     rebind: Callable[[int], dict[str, Any]] = field(default=lambda n: {})  # units in a piece -> changed scalars
+    # Pieces that are not independent but form a chain (the flat scan: every piece starts from the last value of
+    # the piece before): called with the resolved arguments of a piece and of its predecessor (None for the
+    # first) before the piece is launched; the pieces run in order on one stream.
+    chain: Callable[[dict[str, Any], dict[str, Any] | None], None] | None = None
 
 
 @dataclass
@@ -199,9 +203,29 @@ def _histogram(a, grid, variant, stream):
 
 
 # ---- cumsum_kernel(out, in, n_rows, n_cols, stride_in, stride_out, REVERSE, BLOCK_M, BLOCK_N) -----
+def _cumsum_split(a, g):
+    """The flat forward scan cut along the row: a piece is seeded with the last output of the piece before it
+    (the accumulator itself for int32 and float32 outputs, the types the kernel takes a seed for; float16 /
+    bfloat16 outputs are rounded, so those stay in one piece, and so do the other integer widths).  Integer
+    results are the one-piece results bit for bit; float32 results differ from
+    them in the order of the additions, as the one-piece scan's own tile order does from a sequential sum."""
+    if int(a["n_rows"]) != 1 or bool(a["REVERSE"]):
+        return None
+    if _code(a["in_ptr"]) not in (N.I32, N.F32) or _code(a["out_ptr"]) != _code(a["in_ptr"]):
+        return None
+
+    def chain(piece, before):
+        piece["_seed"] = None if before is None else before["out_ptr"][-1:]
+
+    return Split(int(a["n_cols"]), {"in_ptr": 1, "out_ptr": 1}, lambda n: (1, 1, 1),
+                 lambda n: {"n_cols": int(n), "stride_in": int(n), "stride_out": int(n), "BLOCK_N": 1 << max(0, (int(n) - 1).bit_length())},
+                 chain)
+
+
 @register("cumsum_kernel", "out_ptr in_ptr n_rows n_cols stride_in stride_out REVERSE BLOCK_M BLOCK_N",
           "out_ptr in_ptr", "out_ptr", N.K_CUMSUM,
-          extents=lambda a, g: {"out_ptr": int(a["n_rows"]) * int(a["n_cols"])} if int(a["stride_out"]) == int(a["n_cols"]) or int(a["n_rows"]) == 1 else {})
+          extents=lambda a, g: {"out_ptr": int(a["n_rows"]) * int(a["n_cols"])} if int(a["stride_out"]) == int(a["n_cols"]) or int(a["n_rows"]) == 1 else {},
+          split=_cumsum_split)
 def _cumsum(a, grid, variant, stream):
     rows, cols = int(a["n_rows"]), int(a["n_cols"])
     _covers("cumsum_kernel BLOCK_N", int(a["BLOCK_N"]), cols)
@@ -214,8 +238,9 @@ def _cumsum(a, grid, variant, stream):
         raise TypeError(f"cumsum of {interop.element_dtype(a['in_ptr'])} writes "
                         f"{'int32' if want == N.I32 else interop.element_dtype(a['in_ptr'])}, but `out_ptr` is "
                         f"{interop.element_dtype(a['out_ptr'])}")
+    seed = a.get("_seed")  # set by the chained staging of a long NumPy row only
     N.call("enc_cumsum", _ptr(a["in_ptr"]), _ptr(a["out_ptr"]), rows, cols, int(a["stride_in"]),
-           int(a["stride_out"]), int(bool(a["REVERSE"])), dt, None, variant, stream)
+           int(a["stride_out"]), int(bool(a["REVERSE"])), dt, None if seed is None else _ptr(seed), variant, stream)
 
 
 # ---- matmul kernels -------------------------------------------------------------------------------

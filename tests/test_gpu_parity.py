@@ -422,6 +422,17 @@ def test_piecewise_staging_of_numpy_arguments_gives_the_single_piece_result(monk
     q, k, vv = (randn(r, (2, 3, 256, 64), F16) for _ in range(3))  # lse rows of 1 KB keep every piece 256-byte aligned
     same(ops.attention_lse_kernel, ops.attention(q, k, vv, True, return_lse=True),
          ops.attention(torch_of(q), torch_of(k), torch_of(vv), True, return_lse=True))
+    # the flat scan is cut along its one row; every piece is seeded with the last value of the piece before
+    iv = r.integers(-2**31, 2**31, 200003, dtype=np.int64).astype(np.int32)   # wraps modulo 2^32 many times
+    same(ops.cumsum_kernel, ops.cumsum(iv), ops.cumsum(torch_of(iv)))
+    np.testing.assert_array_equal(ops.cumsum(iv), np.cumsum(iv.astype(np.int64)).astype(np.int32))
+    fv = randn(r, (150001,), F32)
+    got = ops.cumsum(fv)
+    assert ops.cumsum_kernel.last_launch.get("pieces", 0) >= 2
+    exact = np.cumsum(fv.astype(np.float64))
+    assert np.abs(got - exact).max() <= max(np.abs(np.cumsum(fv) - exact).max(), 1e-4 * np.abs(exact).max())
+    ops.cumsum(fv, reverse=True)                                # suffix sums are not chained
+    assert "pieces" not in ops.cumsum_kernel.last_launch
     # an array whose flat view is not a view (strided rows) takes the one-piece path
     xs = randn(r, (512, 1024), F32)[:, :512]
     got = ops.softmax(xs)

@@ -404,6 +404,18 @@ def test_piecewise_staging_plan_covers_every_unit_once_on_aligned_boundaries(mon
     assert jit._pipeline_plan(ad, bound, (m, 1, 1), hosts) is None
     # kernels without independent pieces have no split at all
     assert ops.histogram_kernel.adapter().split is None
+    # the flat forward scan of a 32-bit type is cut along its row, each piece seeded by the one before
+    monkeypatch.setattr(jit, "PIPELINE_MIN_BYTES", 1)
+    cad = ops.cumsum_kernel.adapter()
+    v = np.zeros(100003, np.int32)
+    cb = dict(out_ptr=np.empty_like(v), in_ptr=v, n_rows=1, n_cols=v.size, stride_in=v.size, stride_out=v.size, REVERSE=False, BLOCK_M=1, BLOCK_N=131072)
+    csp, cpieces = jit._pipeline_plan(cad, cb, (1, 1, 1), ["out_ptr", "in_ptr"])
+    assert csp.chain is not None and sum(c for _, c in cpieces) == v.size and all(type(c) is int and (u * 4) % 256 == 0 for u, c in cpieces)
+    re = csp.rebind(cpieces[0][1])
+    assert re["n_cols"] == cpieces[0][1] and re["BLOCK_N"] >= re["n_cols"] and csp.grid(cpieces[0][1]) == (1, 1, 1)
+    assert jit._pipeline_plan(cad, dict(cb, REVERSE=True), (1, 1, 1), ["out_ptr", "in_ptr"]) is None
+    h16 = np.zeros(100003, np.float16)
+    assert jit._pipeline_plan(cad, dict(cb, in_ptr=h16, out_ptr=np.empty_like(h16)), (1, 1, 1), ["out_ptr", "in_ptr"]) is None
 
 
 def test_same_name_kernel_with_another_body_is_refused():
