@@ -20,6 +20,10 @@
 // unpacked row in registers: 104 instead of 64 per thread, 5.31 TB/s; capped at 64 it spills, 4.58 TB/s), and looping
 // CTAs one row wide that convert weight and bias once and keep the next rows' loads in flight in registers (about 7
 // instructions per element, but 8 to 16 warps per SM cannot hide the per-row reduction chain: 5.05 TB/s at best).
+// For the short rows of softmax float32 [4096, 1024] (one wave of CTAs, 6.7 us) a warp that owns two rows and issues both
+// rows' loads up front was measured as well: 4.47 against 5.07 TB/s.  The loads of a wave already return spread over
+// the 2.6 us the memory system needs for them, so the arithmetic of early rows overlaps the arrival of late ones as it
+// is, and halving the number of warps only lengthens the arithmetic.
 #include <map>
 #include <mutex>
 #include <tuple>
