@@ -481,6 +481,71 @@ class ClockSampler:
                 "samples": len(rows), "power_w_max": max(float(r[2]) for r in rows if r[2].replace(".", "").isdigit())}
 
 
+class NvmlSampler:
+    """The same readings taken through NVML from a thread of this process, about every millisecond, so that a timed
+    region of a few milliseconds holds several samples (nvidia-smi cannot poll faster than every 100 ms).  Read-only:
+    SM clock, its maximum, power draw and the clock event reasons."""
+
+    NAMES = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+
+    def __init__(self, index: int, period_s: float = 0.001) -> None:
+        import pynvml
+
+        self.nv = pynvml
+        pynvml.nvmlInit()
+        self.h = pynvml.nvmlDeviceGetHandleByIndex(index)
+        self.max_mhz = float(pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM))
+        self.bits = (pynvml.nvmlClocksEventReasonHwSlowdown, pynvml.nvmlClocksEventReasonHwThermalSlowdown,
+                     pynvml.nvmlClocksEventReasonSwThermalSlowdown, pynvml.nvmlClocksEventReasonSwPowerCap)
+        self._read_once()  # fail here, not in the thread, if a query is not supported
+        self.rows: list[tuple[float, float, int]] = []
+        self.period = period_s
+        self.running = True
+        self.thread = threading.Thread(target=self._loop, daemon=True)
+        self.thread.start()
+
+    def _read_once(self) -> tuple[float, float, int]:
+        nv = self.nv
+        return (float(nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM)), nv.nvmlDeviceGetPowerUsage(self.h) / 1e3,
+                int(nv.nvmlDeviceGetCurrentClocksEventReasons(self.h)))
+
+    def _loop(self) -> None:
+        while self.running:
+            try:
+                self.rows.append(self._read_once())
+            except Exception:  # noqa: BLE001 - a failed query must not end the run; the summary shows fewer samples
+                pass
+            time.sleep(self.period)
+
+    def mark(self) -> int:
+        return len(self.rows)
+
+    def stop(self) -> None:
+        self.running = False
+        self.thread.join(timeout=2)
+        try:
+            self.nv.nvmlShutdown()
+        except Exception:  # noqa: BLE001
+            pass
+
+    def summary(self, start: int = 0, end: int | None = None) -> dict:
+        rows = self.rows[start:end] or self.rows
+        if not rows:
+            return {"sm_mhz": None, "sm_max_mhz": self.max_mhz, "reasons": [], "samples": 0}
+        sm = sorted(r[0] for r in rows)
+        reasons = [n for n, b in zip(self.NAMES, self.bits) if any(r[2] & b for r in rows)]
+        return {"sm_mhz": sm[len(sm) // 2], "sm_max_mhz": self.max_mhz, "reasons": reasons, "samples": len(rows),
+                "power_w_max": max(r[1] for r in rows), "how": "NVML, about 1 ms apart"}
+
+
+def make_sampler(index: int):
+    """NVML from this process when it is there, the nvidia-smi poller otherwise."""
+    try:
+        return NvmlSampler(index)
+    except Exception:  # noqa: BLE001 - no pynvml, no NVML, an unsupported query
+        return ClockSampler(index)
+
+
 def visible_gpu_index(local_rank: int) -> int:
     vis = os.environ.get("CUDA_VISIBLE_DEVICES")
     if vis:
@@ -900,7 +965,7 @@ def main() -> None:
     W = workloads(args.scale, (RANK, WORLD) if strong else None)
     if args.workload not in W:
         raise SystemExit(f"workload {args.workload!r} is not available in this build; choose from {sorted(W)}")
-    sampler = ClockSampler(visible_gpu_index(LOCAL_RANK)) if RANK == 0 else None
+    sampler = make_sampler(visible_gpu_index(LOCAL_RANK)) if RANK == 0 else None
     time.sleep(0.3)
     pcie = None if args.no_e2e else measure_pcie()
 
