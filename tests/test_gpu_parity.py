@@ -426,6 +426,8 @@ def test_piecewise_staging_of_numpy_arguments_gives_the_single_piece_result(monk
     iv = r.integers(-2**31, 2**31, 200003, dtype=np.int64).astype(np.int32)   # wraps modulo 2^32 many times
     same(ops.cumsum_kernel, ops.cumsum(iv), ops.cumsum(torch_of(iv)))
     np.testing.assert_array_equal(ops.cumsum(iv), np.cumsum(iv.astype(np.int64)).astype(np.int32))
+    big = r.integers(-2**31, 2**31, 500009, dtype=np.int64).astype(np.int32)  # a 2 MB output is page-locked: copied out per piece
+    same(ops.cumsum_kernel, ops.cumsum(big), ops.cumsum(torch_of(big)))
     fv = randn(r, (150001,), F32)
     got = ops.cumsum(fv)
     assert ops.cumsum_kernel.last_launch.get("pieces", 0) >= 2
