@@ -623,6 +623,13 @@ def all_ranks(ok: bool) -> bool:
     return max_over_ranks(0.0 if ok else 1.0) == 0.0
 
 
+def interop_view(a):
+    """A torch CPU tensor over a NumPy array's memory (bfloat16 included)."""
+    from enceladus_b200.runtime import interop
+
+    return interop._np_as_torch_view(a)
+
+
 def pinned(arrays):
     """Copies of NumPy arrays that live in pinned host memory (views of pinned torch tensors)."""
     import torch
@@ -766,6 +773,25 @@ def bench_workload(wl: dict, steps: int, warmup: int, pk: dict, pk_kind: str, sa
         row["e2e"] = {"value": sum_over_ranks(units) / (dev_ms * 1e-3) / div, "unit": wl["unit"],
                       "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "ms_per_step": dev_ms,
                       "workload_fraction": units / wl["work"]}
+        # the host-array result must be what the same call returns for device-resident copies of the same inputs: bit for
+        # bit (the staged pieces are independent), except the chained float32 scan, whose additions are ordered differently
+        try:
+            dev_in = tuple(interop_view(a).cuda() for a in h)
+            want = wl["run_host"](dev_in)
+            want = want if isinstance(want, tuple) else (want,)
+            torch.cuda.synchronize()
+            same = True
+            for g, w in zip(res, want):
+                gt, wt = interop_view(np.ascontiguousarray(g)), w.cpu().contiguous()
+                if wl["kernel"] == "cumsum" and gt.dtype.is_floating_point:
+                    same = same and bool((gt.double() - wt.double()).abs().max() <= 1e-4 * wt.double().abs().max())
+                else:
+                    same = same and gt.shape == wt.shape and bool(torch.equal(gt.view(torch.uint8), wt.view(torch.uint8)))
+            del dev_in, want
+        except Exception as e:  # noqa: BLE001 - reported, not fatal
+            same = False
+            row["e2e"]["verify_error"] = f"{type(e).__name__}: {e}"
+        row["e2e"]["verified"] = all_ranks(same)
         if pcie:  # the copies alone, both directions overlapped, at the bandwidths measured in this run
             floor_ms = max(h2d / pcie["h2d_gbs"], d2h / pcie["d2h_gbs"], (h2d + d2h) / 2 / pcie["duplex_gbs_each_way"]) / 1e6
             row["e2e"]["pcie_floor_ms"] = floor_ms
@@ -1003,7 +1029,8 @@ def main() -> None:
         c = {"value": round(r["value"], 2), "unit": r["unit"], "frac": round(r["roofline"]["frac"], 4),
              "ms_per_step": round(r["ms_per_step"], 5), "steps": r["steps"], "verified": r["verified"],
              "e2e_value": round(r["e2e"]["value"], 2) if "e2e" in r else None,
-             "e2e_frac": round(r["e2e"]["frac"], 3) if "e2e" in r and "frac" in r["e2e"] else None}
+             "e2e_frac": round(r["e2e"]["frac"], 3) if "e2e" in r and "frac" in r["e2e"] else None,
+             "e2e_verified": r["e2e"].get("verified") if "e2e" in r else None}
         if r.get("collective_in_timed_region"):
             c["collective"] = r["collective_in_timed_region"]
         if r.get("verify_error"):
