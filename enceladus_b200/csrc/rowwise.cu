@@ -15,11 +15,11 @@
 // rounds twice, exp as ex2.approx of a pre-scaled argument, one reciprocal per row instead of a
 // division per element.  Each of these moves a result by a few float32 ulps, far inside the
 // tolerances the results are held to (1e-5 for float32 outputs).
-// Two leaner forms were measured on LayerNorm bf16 [16384, 4096] (17 executed instructions per element here, 5.83 TB/s)
-// and rejected: a path without bounds tests for rows that fill their threads exactly (the compiler then keeps the
-// unpacked row in registers: 104 instead of 64 per thread, 5.31 TB/s; capped at 64 it spills, 4.58 TB/s), and looping
-// CTAs one row wide that convert weight and bias once and keep the next rows' loads in flight in registers (about 7
-// instructions per element, but 8 to 16 warps per SM cannot hide the per-row reduction chain: 5.05 TB/s at best).
+// A leaner form was measured on LayerNorm bf16 [16384, 4096] (17 executed instructions per element, 5.83 TB/s) and
+// rejected: looping CTAs one row wide that convert weight and bias once and keep the next rows' loads in flight in
+// registers (about 7 instructions per element, but 8 to 16 warps per SM cannot hide the per-row reduction chain:
+// 5.05 TB/s at best).  What did pay is a path without bounds tests for rows that fill their threads exactly, once
+// the registers of those instantiations were capped (row_max_regs below).
 // For the short rows of softmax float32 [4096, 1024] (one wave of CTAs, 6.7 us) a warp that owns two rows and issues both
 // rows' loads up front was measured as well: 4.47 against 5.07 TB/s.  The loads of a wave already return spread over
 // the 2.6 us the memory system needs for them, so the arithmetic of early rows overlaps the arrival of late ones as it
@@ -105,17 +105,20 @@ template <typename T, int V> union RowRegs {
 // Statistics and output of one row held in `x`.  WB = true: weight/bias vectors are already in the
 // registers `wreg`/`breg` (persistent CTAs); otherwise they are fetched from global memory (L2-resident).
 // Every thread of the CTA must call this the same number of times (it contains CTA barriers).
-template <typename T, int V, bool VEC, int OP, bool WB>
+// FULL = true: the row is exactly tpr * V vectors wide, so no vector of any thread is cut or past the end and every
+// bounds test disappears (they cost three to four of the seventeen instructions per element).
+template <typename T, int V, bool VEC, int OP, bool WB, bool FULL = false>
 __device__ __forceinline__ void process_row(const RowRegs<T, V> &x, const RowArgs &a, int tpr, int t, int64_t row,
                                             bool live, float *red0, float *red1, float *red2, const uint4 *wreg,
                                             const uint4 *breg) {
     constexpr int NV = Pack<T>::N;
     const float fill = OP == OP_SOFTMAX ? -INFINITY : 0.0f;
     // value (j, e) as float, `fill` beyond the row
+    const int cols = (int)a.cols;
     auto get = [&](int j, float *f) {
-        const int64_t c0 = ((int64_t)j * tpr + t) * NV;
+        const int c0 = (j * tpr + t) * NV;
         if (VEC) {
-            if (c0 < a.cols) {
+            if (FULL || c0 < cols) {
                 Pack<T>::unpack(x.v[j], f);
             } else {
 #pragma unroll
@@ -123,7 +126,7 @@ __device__ __forceinline__ void process_row(const RowRegs<T, V> &x, const RowArg
             }
         } else {
 #pragma unroll
-            for (int e = 0; e < NV; ++e) f[e] = (c0 + e < a.cols) ? to_f32(x.e[j * NV + e]) : fill;
+            for (int e = 0; e < NV; ++e) f[e] = (c0 + e < cols) ? to_f32(x.e[j * NV + e]) : fill;
         }
     };
 
@@ -206,13 +209,13 @@ __device__ __forceinline__ void process_row(const RowRegs<T, V> &x, const RowArg
             float qc = 0.0f;
 #pragma unroll
             for (int j = 0; j < V; ++j) {
-                const int64_t c0 = ((int64_t)j * tpr + t) * NV;
-                if (VEC && c0 >= a.cols) continue;  // a vector is inside the row or entirely past it
+                const int c0 = (j * tpr + t) * NV;
+                if (VEC && !FULL && c0 >= cols) continue;  // a vector is inside the row or entirely past it
                 float f[NV];
                 get(j, f);
 #pragma unroll
                 for (int e = 0; e < NV; ++e) {
-                    const float d = (VEC || c0 + e < a.cols) ? f[e] - mean : 0.0f;
+                    const float d = (VEC || c0 + e < cols) ? f[e] - mean : 0.0f;
                     qc = fmaf(d, d, qc);
                 }
             }
@@ -261,8 +264,8 @@ __device__ __forceinline__ void process_row(const RowRegs<T, V> &x, const RowArg
     const T *br = reinterpret_cast<const T *>(a.b);
 #pragma unroll
     for (int j = 0; j < V; ++j) {
-        const int64_t c0 = ((int64_t)j * tpr + t) * NV;
-        if (c0 >= a.cols) continue;
+        const int c0 = (j * tpr + t) * NV;
+        if (!FULL && c0 >= cols) continue;
         float f[NV], wv[NV], bv[NV];
         get(j, f);
         if (OP != OP_SOFTMAX) {
@@ -275,7 +278,7 @@ __device__ __forceinline__ void process_row(const RowRegs<T, V> &x, const RowArg
             } else {
 #pragma unroll
                 for (int e = 0; e < NV; ++e) {
-                    const bool ok = c0 + e < a.cols;
+                    const bool ok = c0 + e < cols;
                     wv[e] = ok ? to_f32(wr[c0 + e]) : 0.0f;
                     if (OP == OP_LAYERNORM) bv[e] = ok ? to_f32(br[c0 + e]) : 0.0f;
                 }
@@ -303,14 +306,24 @@ __device__ __forceinline__ void process_row(const RowRegs<T, V> &x, const RowArg
         } else {
 #pragma unroll
             for (int e = 0; e < NV; ++e)
-                if (c0 + e < a.cols) yr[c0 + e] = from_f32<T>(o[e]);
+                if (c0 + e < cols) yr[c0 + e] = from_f32<T>(o[e]);
         }
     }
 }
 
 // One CTA per group of blockDim/tpr rows; the rows go straight from global memory to registers.
+// Register cap of an instantiation.  With the fast path above the compiler would keep a whole unpacked row in registers
+// (104 per thread for LayerNorm bf16, 8 vectors), which costs more in resident warps than the saved unpacking brings
+// back, and capped at 64 it spills.  Measured per cap (TB/s, default variants): LayerNorm bf16 [16384, 4096]: 4.58 at
+// 64, 5.40 at 72, 5.92 at 80, 5.76 at 96, 5.31 uncapped (5.81 before the fast path); softmax float32 [4096, 1024]:
+// 5.03, 5.28, 5.17, 5.16, 5.18 (5.06 before).  Rows of at most 4 vectors per thread need no cap, and 16 vectors (64
+// registers of packed row data) need all 128.
+template <typename T, int V, int OP> constexpr int row_max_regs() {
+    return V != 8 ? 128 : (OP == OP_SOFTMAX && sizeof(T) == 4 ? 72 : 80);
+}
+
 template <typename T, int V, bool VEC, int OP>
-__global__ void __launch_bounds__(512) row_kernel(RowArgs a) {
+__global__ void __maxnreg__((row_max_regs<T, V, OP>())) row_kernel(RowArgs a) {
     constexpr int NV = Pack<T>::N;
     __shared__ float red0[MAX_WARPS], red1[MAX_WARPS], red2[MAX_WARPS];
     const int tpr = a.tpr;
@@ -325,15 +338,22 @@ __global__ void __launch_bounds__(512) row_kernel(RowArgs a) {
     grid_dependency_wait();  // launched with launch_overlapped(): nothing above touches global memory
 
     RowRegs<T, V> x;
+    const int cols = (int)a.cols;
+    if (VEC && cols == tpr * (V * NV)) {  // every vector of every thread is inside the row: no bounds tests anywhere
+#pragma unroll
+        for (int j = 0; j < V; ++j) x.v[j] = ld_stream(xr + (j * tpr + t) * NV);
+        process_row<T, V, VEC, OP, false, true>(x, a, tpr, t, row, live, red0, red1, red2, nullptr, nullptr);
+        return;
+    }
 #pragma unroll
     for (int j = 0; j < V; ++j) {
-        const int64_t c0 = ((int64_t)j * tpr + t) * NV;
+        const int c0 = (j * tpr + t) * NV;
         if (VEC) {
-            if (c0 < a.cols) x.v[j] = ld_stream(xr + c0);
+            if (c0 < cols) x.v[j] = ld_stream(xr + c0);
         } else {
 #pragma unroll
             for (int e = 0; e < NV; ++e)
-                if (c0 + e < a.cols) x.e[j * NV + e] = xr[c0 + e];
+                if (c0 + e < cols) x.e[j * NV + e] = xr[c0 + e];
         }
     }
     process_row<T, V, VEC, OP, false>(x, a, tpr, t, row, live, red0, red1, red2, nullptr, nullptr);
@@ -577,15 +597,15 @@ int launch_rows(RowArgs a, int variant, cudaStream_t st, const char *name) {
     if (a.rows == 0 || a.cols == 0) return ENC_OK;
     if (a.rows > 0x7fffffffLL) return fail(ENC_ERR_UNSUPPORTED, "%s: more than 2^31-1 rows", name);
     if (variant >= ROW_VARIANTS) return fail(ENC_ERR_BAD_ARG, "%s: variant %d out of range", name, variant);
-    // measured: RMSNorm bf16 [16384, 4096] is fastest with four times the minimum threads per row (97% of the copy
-    // bandwidth against 95%), LayerNorm with twice, softmax fp32 [4096, 1024] and [4096, 4096] with the minimum.
-    // float32 rows of 4096 (16 KB): LayerNorm with the minimum and 256-thread CTAs (5.66 against 5.15 TB/s), RMSNorm
-    // with twice the minimum (6.2 against 5.1 TB/s).  Wide 16-bit softmax rows take four times the minimum, 32 elements
-    // per thread with the exponentials kept in registers (4.9 against 3.8 TB/s with the minimum and recomputation).
+    // measured (TB/s): RMSNorm bf16 [16384, 4096] is fastest with four times the minimum threads per row (6.5 against
+    // 6.1), LayerNorm bf16 with twice (5.93 against 4.86 and 4.52), softmax fp32 [4096, 1024] and [4096, 4096] with the
+    // minimum (5.29, 6.33).  float32 rows of 4096 (16 KB): LayerNorm and RMSNorm with the minimum, 8 vectors per thread
+    // (5.98 and 6.20 against 5.24 and 5.83 with twice).  Wide 16-bit softmax rows take twice the minimum, 64 elements
+    // per thread with the exponentials kept in registers (5.07 against 4.57 with four times and 4.46 with the minimum).
     if (variant < 0) {
-        if (OP == OP_SOFTMAX) variant = sizeof(T) == 2 && a.cols > 2048 ? 6 : 0;
-        else if (OP == OP_LAYERNORM) variant = sizeof(T) == 4 && a.cols >= 2048 ? 1 : kAutoVariant;
-        else variant = sizeof(T) == 4 ? 3 : (a.cols * (int64_t)sizeof(T) >= 4096 ? 6 : kAutoVariant);
+        if (OP == OP_SOFTMAX) variant = sizeof(T) == 2 && a.cols > 2048 ? 3 : 0;
+        else if (OP == OP_LAYERNORM) variant = sizeof(T) == 4 && a.cols >= 2048 ? 0 : kAutoVariant;
+        else variant = sizeof(T) == 4 ? (a.cols >= 2048 ? 0 : 3) : (a.cols * (int64_t)sizeof(T) >= 4096 ? 6 : kAutoVariant);
     }
     const bool pipe = variant >= 12;
     const int shift = (variant % 12) / 3;
