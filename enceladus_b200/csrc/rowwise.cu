@@ -624,9 +624,11 @@ int launch_rows(RowArgs a, int variant, cudaStream_t st, const char *name) {
     }
     a.tpr = (int)tpr64;
     if (cta < a.tpr) cta = a.tpr;
-    // LayerNorm's CTA-wide agreement on the ill-conditioned branch costs a barrier per row unless the CTA holds one row:
-    // a row of two warps gets a CTA of its own at the smallest CTA size (bf16 [16384, 4096]: 6.01 against 5.93 TB/s)
-    if (OP == OP_LAYERNORM && !pipe && a.tpr == 64 && variant % 3 == 0) cta = 64;
+    // The reductions of a row that spans two warps are CTA barriers, which hold up the other rows of the CTA as well,
+    // and LayerNorm's CTA-wide agreement on the ill-conditioned branch costs a second barrier per row unless the CTA
+    // holds one row: at the smallest CTA size such a row gets a CTA of its own (LayerNorm bf16 [16384, 4096]: 6.01
+    // against 5.93 TB/s; softmax fp16 [4096, 4096]: 5.30 against 5.11).
+    if (!pipe && a.tpr == 64 && variant % 3 == 0) cta = 64;
     int v = next_pow2(cdiv(a.cols, (int64_t)a.tpr * NV));
     const bool vec = a.cols % NV == 0 && a.stride_x % NV == 0 && a.stride_y % NV == 0 &&
                      aligned16(a.x) && aligned16(a.y) &&
@@ -653,7 +655,7 @@ template <int OP> int dispatch(const RowArgs &a, int dtype, int variant, void *s
 
 int row_variants() { return ROW_VARIANTS; }
 void row_variant_info(int v, char *out, size_t n) {
-    snprintf(out, n, "threads_per_row=base*%d cta_threads=%d %s (base = fewest threads whose registers hold the row, min 32; a LayerNorm row of 64 threads takes a 64-thread CTA at cta_threads=128)",
+    snprintf(out, n, "threads_per_row=base*%d cta_threads=%d %s (base = fewest threads whose registers hold the row, min 32; a row of 64 threads takes a 64-thread CTA at cta_threads=128)",
              1 << ((v % 12) / 3), 128 << (v % 3), v >= 12 ? "persistent CTAs fed by a cp.async.bulk ring" : "direct loads");
 }
 
