@@ -321,7 +321,11 @@ __device__ __forceinline__ void process_row(const RowRegs<T, V> &x, const RowArg
 // registers of packed row data) need all 128.
 template <typename T, int V, int OP> constexpr int row_max_regs() {
     if (V == 4 && OP == OP_RMSNORM && sizeof(T) == 2) return 56;  // RMSNorm bf16 [16384, 4096]: 6.67 against 6.50 TB/s uncapped (6.63 at 48, 5.04 at 40)
-    return V != 8 ? 128 : (OP == OP_SOFTMAX && sizeof(T) == 4 ? 72 : 80);
+    if (V != 8) return 128;
+    if (OP == OP_SOFTMAX) return sizeof(T) == 4 ? 72 : 80;
+    // LayerNorm fp16 [4096, 4096]: 4.73 at 88 against 4.48 at 80 (bf16 [16384, 4096] the same at both); RMSNorm fp32
+    // [4096, 4096]: 6.29 against 6.19; LayerNorm fp32: 5.92 against 5.97
+    return (OP == OP_LAYERNORM) == (sizeof(T) == 2) ? 88 : 80;
 }
 
 template <typename T, int V, bool VEC, int OP>
