@@ -53,7 +53,7 @@ ROTATE_BYTES = 1 << 30  # total size of the rotating buffer sets for workloads s
 # workloads were captured at 2^27 elements (few GB on the device under the profiler) and are scaled by
 # the element count: their traffic is proportional to it.
 NCU_TRAFFIC: dict[str, float | None] = {
-    "layernorm_bf16_16384x4096": 224_167_424,       # profiles/layernorm.md
+    "layernorm_bf16_16384x4096": 219_303_936,       # profiles/layernorm.md
     "rmsnorm_bf16_16384x4096": 216_850_688,         # profiles/rmsnorm.md
     "softmax_f32_4096x1024": 16_802_304,            # profiles/softmax.md (the 16 MiB output stays in L2)
     "gelu_tanh_f32_2p28": 2_100_776_000,            # profiles/gelu.md
