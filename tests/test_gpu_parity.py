@@ -111,6 +111,25 @@ def test_layernorm_shapes(oracle, dt, shape):
     assert_close(host(rstd), wr, atol=1e-5, rtol=1e-5)
 
 
+@pytest.mark.parametrize("dt", [BF16, F16, F32], ids=str)
+@pytest.mark.parametrize("shape", [(77, 4096), (77, 4088), (5, 2056), (3, 2048), (130, 1024), (9, 8192)], ids=str)
+def test_rows_that_fill_their_threads_and_rows_that_do_not(oracle, dt, shape):
+    """Rows that are exactly threads x vectors wide take the kernels' path without bounds tests and, when they span two
+    warps, a CTA of their own; rows a vector or more short of that, and odd row counts, take the general path.  All
+    three row kernels, every dtype, against the oracle."""
+    r = np.random.default_rng(shape[0] * 31 + shape[1])
+    x = randn(r, shape, dt)
+    w = (1 + 0.1 * r.standard_normal(shape[1])).astype(np.float32).astype(dt)
+    b = (0.1 * r.standard_normal(shape[1])).astype(np.float32).astype(dt)
+    y, mean, rstd = ops.layernorm(torch_of(x), torch_of(w), torch_of(b))
+    wy, wm, wr = oracle.layernorm(x, w, b)
+    assert_close(host(y), wy, atol=1e-4 if dt == F32 else None, what="layernorm")
+    assert_close(host(mean), wm, atol=1e-5, rtol=1e-5)
+    assert_close(host(rstd), wr, atol=1e-5, rtol=1e-5)
+    assert_close(host(ops.rmsnorm(torch_of(x), torch_of(w))), oracle.rmsnorm(x, w), what="rmsnorm")
+    assert_close(host(ops.softmax(torch_of(x))), oracle.softmax(x), what="softmax")
+
+
 def test_rmsnorm_golden():
     g = load_golden("rmsnorm")
     for k in [k[:-2] for k in g if k.endswith("_x")]:
