@@ -903,21 +903,25 @@ attention_ts64_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
         const int64_t tile_m0 = m0 + t * BM;
         float m_ref = -INFINITY, l = 0.0f;
         bool ok = true;
+        // block bookkeeping in 32 bits (this kernel takes sequences below 2^31): a block needs its mask when it reaches
+        // past `bound`; `last` is the last key this row sees
+        const int seq_i = (int)a.seq;
+        const int bound = a.causal && (int)tile_m0 < seq_i ? (int)tile_m0 : seq_i;
+        const int last_i = a.causal && row < a.seq ? (int)row : seq_i - 1;
         for (int j = 0; j < my_nkv && ok; ++j) {
             const int b = j & 1;
             ok = mbar_wait(&s_full[t * 2 + b], (j >> 1) & 1, abort);
             if (!ok) break;
             tc_fence_after();
-            const int64_t n0 = (int64_t)j * BNK;
-            const bool need_mask = (n0 + BNK > a.seq) || (a.causal && n0 + BNK > tile_m0);
+            const int n0 = j * BNK;
+            const bool need_mask = n0 + BNK > bound;
             uint32_t sv[2][32];
 #pragma unroll
             for (int c = 0; c < 2; ++c) tmem_ld_32x32(t_s + b * BNK + c * 32, sv[c]);
             tmem_ld_wait();
             float alpha;
             bool rescale;
-            const int64_t last = a.causal && row < a.seq ? row : a.seq - 1;  // last key this row sees
-            softmax_row_lim<2, kPolyPairs>(sv, a.qk_scale, need_mask, (int)(last - n0), m_ref, l, alpha, rescale);
+            softmax_row_lim<2, kPolyPairs>(sv, a.qk_scale, need_mask, last_i - n0, m_ref, l, alpha, rescale);
             if (j > 0 && __any_sync(0xffffffffu, rescale)) {
                 // O_t must be quiescent: P_t(j-1) V complete (P_t(j) V is not issued before this thread's arrival below)
                 ok = mbar_wait(&pv_done[t * 2 + (b ^ 1)], ((j - 1) >> 1) & 1, abort);
